@@ -1,0 +1,67 @@
+"""Seeded synthetic inputs for the block-attention path.
+
+They stand in for real model activations: the reference itself checks this path only on synthetic N(0,1) data
+(engine/tests/test_attn.cu:20-27 draws Q/K/V ~ N(0,1) and turns one K channel into an outlier). Here Q, K, V are
+N(0,1) rounded to fp16 and four fixed K channels of every kv head are multiplied by 8.
+
+Everything is drawn from numpy's counter-based Philox generator keyed by (seed, stream id), so any host in any
+process regenerates identical bytes for a given (sequence, layer, kind).
+"""
+from __future__ import annotations
+
+import numpy as np
+
+D, BLK, NKV, NQH = 128, 32, 4, 16
+REC_BYTES = 4736
+OUTLIER_CHANNELS = (5, 37, 70, 101)
+OUTLIER_GAIN = 8.0
+BASE_SEED = 7
+
+_KIND = {"ctx_k": 1, "ctx_v": 2, "q": 3, "fresh_k": 4, "fresh_v": 5}
+
+
+def _rng(seed: int, seq: int, layer: int, kind: str) -> np.random.Generator:
+    return np.random.Generator(np.random.Philox(key=[seed, (seq << 24) | (layer << 8) | _KIND[kind]]))
+
+
+def _normal16(g: np.random.Generator, shape) -> np.ndarray:
+    return g.standard_normal(shape, dtype=np.float32).astype(np.float16)
+
+
+def _add_outliers(K: np.ndarray) -> np.ndarray:
+    Kf = K.astype(np.float32)
+    Kf[..., list(OUTLIER_CHANNELS)] *= OUTLIER_GAIN
+    return Kf.astype(np.float16)
+
+
+def context_blocks(nblocks: int, seq: int = 0, layer: int = 0, seed: int = BASE_SEED):
+    """fp16 K, V of `nblocks` committed blocks: [nblocks][32][4][128] each (K carries the outlier channels)."""
+    K = _add_outliers(_normal16(_rng(seed, seq, layer, "ctx_k"), (nblocks, BLK, NKV, D)))
+    V = _normal16(_rng(seed, seq, layer, "ctx_v"), (nblocks, BLK, NKV, D))
+    return K, V
+
+
+def query_blocks(nq: int, seq: int = 0, layer: int = 0, seed: int = BASE_SEED):
+    """Q [nq][32][16][128] and the fresh K, V [nq][32][4][128] of nq query blocks, fp16."""
+    Q = _normal16(_rng(seed, seq, layer, "q"), (nq, BLK, NQH, D))
+    Kf = _add_outliers(_normal16(_rng(seed, seq, layer, "fresh_k"), (nq, BLK, NKV, D)))
+    Vf = _normal16(_rng(seed, seq, layer, "fresh_v"), (nq, BLK, NKV, D))
+    return Q, Kf, Vf
+
+
+def ragged_lengths(nseq: int, lo_tokens: int = 128, hi_tokens: int = 32768, seed: int = BASE_SEED) -> np.ndarray:
+    """Committed context lengths in blocks, uniform over the multiples of 32 in [lo_tokens, hi_tokens]."""
+    g = np.random.Generator(np.random.Philox(key=[seed, 0xA66ED]))
+    return g.integers(lo_tokens // BLK, hi_tokens // BLK + 1, size=nseq).astype(np.int32)
+
+
+def algorithmic_bytes(nblocks: int, int8_out: bool = False) -> int:
+    """Bytes one (sequence, layer, 32-token query block) must move at `nblocks` committed blocks: the packed
+    records of the 4 kv heads, Q, the fresh K and V, and the output."""
+    out = 69632 if int8_out else 131072
+    return nblocks * NKV * REC_BYTES + 131072 + 65536 + out
+
+
+def algorithmic_flops(nblocks: int) -> int:
+    """QK^T + PV flops (multiply-add = 2) for one (sequence, layer, query block)."""
+    return 4 * BLK * NQH * D * (nblocks * BLK + BLK)
