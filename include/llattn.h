@@ -1,0 +1,153 @@
+/*
+ * llattn — block-diffusion attention over the int4 "4c/4" KV cache and its block-commit quantiser, for sm_100a.
+ *
+ * C ABI of libllattn.so. Plain pointers and sizes only. Every function returns an llattn_status (0 = ok) and never
+ * exits the process; llattn_last_error() gives the message of the last failure on the calling thread. Unless a
+ * parameter says "host", data pointers are DEVICE pointers owned by the caller. `stream` is a cudaStream_t passed
+ * as void* (NULL = the default stream). A context may be used from any thread, one call at a time.
+ *
+ * Each entry point names the interface of the reference engine (patrickbdevaney/llada2-orin-cuda) it stands in
+ * for, as file:line of that project.
+ *
+ * Layouts (engine/attn.cu:51-64 and :3-7,22-25):
+ *   Q        [nq_total][32 tok][16 heads][128] fp16, after q-norm and RoPE
+ *   Kf, Vf   [nq_total][32 tok][4 heads][128]  fp16, the fresh K/V of the query blocks
+ *   record   4736 bytes per (kv head, 32-token block): K codes [32][64], K scale fp16[128], K min fp16[128],
+ *            V codes [32][64], V scale fp16[32], V min fp16[32]; value = code * scale + min
+ *   cache    one layer of one sequence, [4 heads][max_blocks][4736]
+ */
+#ifndef LLATTN_H
+#define LLATTN_H
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#define LLATTN_HEAD_DIM 128
+#define LLATTN_BLOCK_TOKENS 32
+#define LLATTN_KV_HEADS 4
+#define LLATTN_Q_HEADS 16
+#define LLATTN_RECORD_BYTES 4736 /* attn::KV_BLOCK_BYTES, engine/attn.cu:23 */
+#define LLATTN_KOFF_META 2048    /* attn::KOFF_META */
+#define LLATTN_VOFF 2560         /* attn::VOFF */
+#define LLATTN_VOFF_META 4608    /* attn::VOFF_META */
+
+typedef enum llattn_status {
+    LLATTN_OK = 0,
+    LLATTN_EINVAL = 1,  /* bad argument (null pointer, negative count, misaligned pointer, index out of range) */
+    LLATTN_ECUDA = 2,   /* a CUDA runtime call failed */
+    LLATTN_ENOMEM = 3,  /* an allocation failed, or a caller-provided buffer is too small */
+    LLATTN_EDEVICE = 4  /* a kernel reported a wait that ran out (see llattn_device_status) */
+} llattn_status;
+
+const char* llattn_version(void);
+const char* llattn_last_error(void);
+
+/* ---- split policy of the reference, kept for callers that size buffers with it.
+ * attn::pick_bpc (engine/attn.cu:361-364) and attn::chunks_for (engine/attn.cu:67). */
+int llattn_pick_bpc(int nblocks, int nbatch);
+int llattn_chunks_for(int nblocks, int blocks_per_chunk);
+
+/* ---- block commit.
+ * Stands in for attn::kv_commit<<<dim3(4, nb), 128, 0, st>>>(Kf, Vf, cache, max_blocks, blk)
+ * (engine/attn.cu:369; call sites engine/engine.cu:591 and :656): block j of Kf/Vf becomes record blk + j of every
+ * kv head of `cache`. Output bytes are identical to the reference kernel's. */
+int llattn_kv_commit(const void* Kf, const void* Vf, void* cache, int max_blocks, int blk, int nb, void* stream);
+
+/* Same quantiser into a record pool: block j, head h goes to record pages[j * 4 + h] of `pool`
+ * (`pages` is a device array of nb * 4 indices). No counterpart in the reference, whose cache is contiguous. */
+int llattn_kv_commit_paged(const void* Kf, const void* Vf, void* pool, const int32_t* pages, int nb, void* stream);
+
+/* ---- the reference operator pair on caller-owned buffers.
+ * llattn_args mirrors attn::Args (engine/attn.cu:51-64) field for field. */
+typedef struct llattn_args {
+    const void* Q;
+    const void* Kf;
+    const void* Vf;
+    const void* cache;
+    int max_blocks;
+    int nblocks;          /* committed blocks visible to query block 0; block j sees nblocks + j */
+    int blocks_per_chunk;
+    int nchunks;          /* chunk slots per (query block, kv head) in the partial buffers */
+    float scale;          /* 1/sqrt(128) */
+    float* Opart;         /* [nb][4][nchunks][128][128] un-normalised */
+    float* Mpart;         /* [nb][4][nchunks][128] reference maximum, log2 units */
+    float* Lpart;         /* [nb][4][nchunks][128] */
+} llattn_args;
+
+/* Stands in for attn::attn_partial<<<dim3(4, nchunks, nb), ATT_NTH, SMEM_BYTES, st>>>(args)
+ * (engine/attn.cu:145; call sites engine/engine.cu:431 and :596). `err_word` is a device int the kernel ORs an
+ * error code into when a bounded wait runs out (may be NULL). */
+int llattn_attn_partial(const llattn_args* args, int nb, int* err_word, void* stream);
+
+/* Stands in for attn::attn_combine<<<dim3(4, 16, nb), 256, 0, st>>>(Opart, Mpart, Lpart, nchunks, nblocks, bpc,
+ * O, q8, s8, sum8) (engine/attn.cu:319; call sites engine/engine.cu:432 and :598). With q8 non-null the int8
+ * activation form (fragment order, per-head scale, integer sum) is written and O is not, as in the reference. */
+int llattn_attn_combine(const float* Opart, const float* Mpart, const float* Lpart, int nchunks, int nblocks,
+                        int blocks_per_chunk, void* O, int8_t* q8, float* s8, int32_t* sum8, int nb, void* stream);
+
+/* ---- batched path: many independent sequences, ragged lengths, contiguous or paged caches.
+ * No counterpart in the reference (it serves one sequence); each sequence gets exactly what
+ * attn_partial + attn_combine give it at engine/engine.cu:429-432 (decode) or :594-598 (prefill). */
+typedef struct llattn_ctx llattn_ctx;
+typedef struct llattn_plan llattn_plan;
+
+typedef struct llattn_seq {
+    const void* cache;     /* device: this layer's cache of the sequence, or the record pool when pages != NULL */
+    const int32_t* pages;  /* device: NULL, or [4][head_stride] record indices into the pool */
+    int32_t head_stride;   /* contiguous: max_blocks; paged: entries per kv head in `pages` */
+    int32_t nblocks;       /* committed blocks visible to the sequence's first query block */
+    int32_t nq;            /* query blocks in this call: 1 for a denoising step, up to 16 for a prefill pass */
+    int32_t q_first;       /* index of its first query block in Q / Kf / Vf and in the outputs */
+} llattn_seq;
+
+typedef struct llattn_io {
+    const void* Q;
+    const void* Kf;
+    const void* Vf;
+    void* O16;      /* [nq_total*32][16][128] fp16, or NULL */
+    float* O32;     /* same shape fp32, or NULL */
+    float* LSE;     /* [nq_total*32][16] natural-log sum of exponentials of the scaled scores, or NULL */
+    int8_t* q8;     /* [nq_total*32][2048] int8 activations in fragment order, or NULL (engine/attn.cu:346-357) */
+    float* s8;      /* [nq_total*32][16] */
+    int32_t* sum8;  /* [nq_total*32][16] */
+    float scale;    /* 0 -> 1/sqrt(128) */
+} llattn_io;
+
+typedef struct llattn_plan_stats {
+    int32_t nseq, nq_total, nitems, nslots, nctas;
+    int64_t total_units;       /* records + fresh blocks over all (query block, kv head) pairs */
+    int64_t max_cta_units;     /* units of the busiest CTA */
+    size_t workspace_bytes;    /* partial-result scratch the plan needs (owned by the context) */
+} llattn_plan_stats;
+
+int llattn_create(int device, llattn_ctx** out);
+void llattn_destroy(llattn_ctx* ctx);
+
+/* Builds the work list for `nseq` sequences (host array) and uploads it; allocates, so not for use inside stream
+ * capture. `nctas` <= 0 means one CTA per SM. The plan stays valid until the lengths or pointers change. */
+int llattn_plan_create(llattn_ctx* ctx, const llattn_seq* seqs_host, int nseq, int nctas, llattn_plan** out);
+void llattn_plan_destroy(llattn_plan* plan);
+int llattn_plan_get_stats(const llattn_plan* plan, llattn_plan_stats* out);
+
+/* One attention pass over every sequence of the plan: kernel launches only (two), no allocation, no host sync. */
+int llattn_attention(llattn_ctx* ctx, const llattn_plan* plan, const llattn_io* io, void* stream);
+
+/* The same pass one kernel at a time, for per-kernel timing: parts = 1 runs only the tile kernel (partials into the
+ * context's scratch), 2 only the merge of the partials already there, 3 both (= llattn_attention). */
+int llattn_attention_parts(llattn_ctx* ctx, const llattn_plan* plan, const llattn_io* io, int parts, void* stream);
+
+/* Same, with Q/Kf/Vf and the requested outputs in HOST memory (pinned for asynchronous copies): copies in, runs,
+ * copies out, on `stream`. The KV cache stays on the device, as in the reference engine. */
+int llattn_attention_host(llattn_ctx* ctx, const llattn_plan* plan, const llattn_io* io_host, void* stream);
+
+/* Reads (and clears) the context's device error word; synchronises `stream`. 0 = no kernel wait ran out. */
+int llattn_device_status(llattn_ctx* ctx, void* stream, int* code);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* LLATTN_H */

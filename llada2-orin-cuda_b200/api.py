@@ -1,0 +1,255 @@
+"""ctypes binding of libllattn.so and the host-side mirror of the reference's `attn` operator interface.
+
+Names follow the reference (engine/attn.cu): `Args`, `pick_bpc`, `chunks_for`, `kv_commit`, `attn_partial`,
+`attn_combine`, the record constants. `Context` / `Plan` / `attention` are the batched path (many sequences, ragged
+lengths, paged or contiguous caches). Device memory is held in torch tensors; only their data pointers cross the
+C ABI. There is no fallback: loading fails loudly when the CUDA library has not been built.
+"""
+from __future__ import annotations
+
+import ctypes
+import os
+from ctypes import POINTER, Structure, byref, c_char_p, c_float, c_int, c_int32, c_int64, c_size_t, c_void_p
+from dataclasses import dataclass
+from typing import Optional, Sequence
+
+HERE = os.path.dirname(os.path.abspath(__file__))
+LIB_PATH = os.path.join(HERE, "libllattn.so")
+
+D, BLK, NKV, NQH = 128, 32, 4, 16
+KV_BLOCK_BYTES, KOFF_META, VOFF, VOFF_META = 4736, 2048, 2560, 4608
+SCALE = 0.08838834764831845  # 1/sqrt(128), the constant engine/engine.cu:430 passes
+
+OK, EINVAL, ECUDA, ENOMEM, EDEVICE = 0, 1, 2, 3, 4
+
+EXPORTS = (
+    "llattn_version", "llattn_last_error", "llattn_pick_bpc", "llattn_chunks_for", "llattn_kv_commit",
+    "llattn_kv_commit_paged", "llattn_attn_partial", "llattn_attn_combine", "llattn_create", "llattn_destroy",
+    "llattn_plan_create", "llattn_plan_destroy", "llattn_plan_get_stats", "llattn_attention",
+    "llattn_attention_parts", "llattn_attention_host", "llattn_device_status",
+)
+
+
+class LlattnError(RuntimeError):
+    def __init__(self, code: int, msg: str):
+        super().__init__(f"llattn status {code}: {msg}")
+        self.code = code
+
+
+class _Args(Structure):
+    _fields_ = [("Q", c_void_p), ("Kf", c_void_p), ("Vf", c_void_p), ("cache", c_void_p), ("max_blocks", c_int),
+                ("nblocks", c_int), ("blocks_per_chunk", c_int), ("nchunks", c_int), ("scale", c_float),
+                ("Opart", c_void_p), ("Mpart", c_void_p), ("Lpart", c_void_p)]
+
+
+class _Seq(Structure):
+    _fields_ = [("cache", c_void_p), ("pages", c_void_p), ("head_stride", c_int32), ("nblocks", c_int32),
+                ("nq", c_int32), ("q_first", c_int32)]
+
+
+class _IO(Structure):
+    _fields_ = [("Q", c_void_p), ("Kf", c_void_p), ("Vf", c_void_p), ("O16", c_void_p), ("O32", c_void_p),
+                ("LSE", c_void_p), ("q8", c_void_p), ("s8", c_void_p), ("sum8", c_void_p), ("scale", c_float)]
+
+
+class PlanStats(Structure):
+    _fields_ = [("nseq", c_int32), ("nq_total", c_int32), ("nitems", c_int32), ("nslots", c_int32), ("nctas", c_int32),
+                ("total_units", c_int64), ("max_cta_units", c_int64), ("workspace_bytes", c_size_t)]
+
+
+_lib = None
+
+
+def lib() -> ctypes.CDLL:
+    """Loads libllattn.so (built by build.py). Raises if it is missing: there is no other implementation."""
+    global _lib
+    if _lib is None:
+        if not os.path.exists(LIB_PATH):
+            raise FileNotFoundError(f"{LIB_PATH} is not built; run `python __graft_entry__.py` or build.build()")
+        L = ctypes.CDLL(LIB_PATH)
+        L.llattn_version.restype = c_char_p
+        L.llattn_last_error.restype = c_char_p
+        L.llattn_pick_bpc.argtypes = [c_int, c_int]
+        L.llattn_chunks_for.argtypes = [c_int, c_int]
+        L.llattn_kv_commit.argtypes = [c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_void_p]
+        L.llattn_kv_commit_paged.argtypes = [c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_void_p]
+        L.llattn_attn_partial.argtypes = [POINTER(_Args), c_int, c_void_p, c_void_p]
+        L.llattn_attn_combine.argtypes = [c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_void_p, c_void_p,
+                                          c_void_p, c_void_p, c_int, c_void_p]
+        L.llattn_create.argtypes = [c_int, POINTER(c_void_p)]
+        L.llattn_destroy.argtypes = [c_void_p]
+        L.llattn_destroy.restype = None
+        L.llattn_plan_create.argtypes = [c_void_p, POINTER(_Seq), c_int, c_int, POINTER(c_void_p)]
+        L.llattn_plan_destroy.argtypes = [c_void_p]
+        L.llattn_plan_destroy.restype = None
+        L.llattn_plan_get_stats.argtypes = [c_void_p, POINTER(PlanStats)]
+        L.llattn_attention.argtypes = [c_void_p, c_void_p, POINTER(_IO), c_void_p]
+        L.llattn_attention_parts.argtypes = [c_void_p, c_void_p, POINTER(_IO), c_int, c_void_p]
+        L.llattn_attention_host.argtypes = [c_void_p, c_void_p, POINTER(_IO), c_void_p]
+        L.llattn_device_status.argtypes = [c_void_p, c_void_p, POINTER(c_int)]
+        _lib = L
+    return _lib
+
+
+def _check(rc: int) -> None:
+    if rc != OK:
+        raise LlattnError(rc, lib().llattn_last_error().decode())
+
+
+def _ptr(t) -> Optional[int]:
+    """Data pointer of a torch tensor (device or host) or None."""
+    if t is None:
+        return None
+    if not t.is_contiguous():
+        raise ValueError("tensors crossing the C ABI must be contiguous")
+    return t.data_ptr()
+
+
+def _stream(stream) -> Optional[int]:
+    if stream is None:
+        import torch
+        return torch.cuda.current_stream().cuda_stream
+    return getattr(stream, "cuda_stream", stream)
+
+
+# ------------------------------------------------------------------ reference policy helpers
+
+def pick_bpc(nblocks: int, nbatch: int) -> int:
+    """attn::pick_bpc (engine/attn.cu:361-364)."""
+    return lib().llattn_pick_bpc(nblocks, nbatch)
+
+
+def chunks_for(nblocks: int, bpc: int) -> int:
+    """attn::chunks_for (engine/attn.cu:67)."""
+    return lib().llattn_chunks_for(nblocks, bpc)
+
+
+# ------------------------------------------------------------------ commit
+
+def kv_commit(Kf, Vf, cache, max_blocks: int, blk: int, stream=None) -> None:
+    """attn::kv_commit<<<dim3(4, nb), 128>>>(Kf, Vf, cache, max_blocks, blk) (engine/attn.cu:369).
+    Kf, Vf: fp16 [nb][32][4][128]; cache: uint8 [4][max_blocks][4736]."""
+    nb = Kf.shape[0] if Kf.dim() == 4 else 1
+    _check(lib().llattn_kv_commit(_ptr(Kf), _ptr(Vf), _ptr(cache), max_blocks, blk, nb, _stream(stream)))
+
+
+def kv_commit_paged(Kf, Vf, pool, pages, stream=None) -> None:
+    """Same quantiser into a record pool: pages is an int32 device tensor [nb][4] of record indices."""
+    nb = Kf.shape[0]
+    if pages.numel() != nb * NKV:
+        raise ValueError("pages must hold nb * 4 indices")
+    _check(lib().llattn_kv_commit_paged(_ptr(Kf), _ptr(Vf), _ptr(pool), _ptr(pages), nb, _stream(stream)))
+
+
+# ------------------------------------------------------------------ the reference operator pair
+
+@dataclass
+class Args:
+    """attn::Args (engine/attn.cu:51-64); tensors instead of raw pointers."""
+    Q: object
+    Kf: object
+    Vf: object
+    cache: object
+    max_blocks: int
+    nblocks: int
+    blocks_per_chunk: int
+    nchunks: int
+    scale: float
+    Opart: object
+    Mpart: object
+    Lpart: object
+
+
+def attn_partial(a: Args, nb: int = 1, err_word=None, stream=None) -> None:
+    """attn::attn_partial<<<dim3(4, nchunks, nb)>>>(a) (engine/attn.cu:145)."""
+    s = _Args(_ptr(a.Q), _ptr(a.Kf), _ptr(a.Vf), _ptr(a.cache), a.max_blocks, a.nblocks, a.blocks_per_chunk, a.nchunks,
+              a.scale, _ptr(a.Opart), _ptr(a.Mpart), _ptr(a.Lpart))
+    _check(lib().llattn_attn_partial(byref(s), nb, _ptr(err_word), _stream(stream)))
+
+
+def attn_combine(Opart, Mpart, Lpart, nchunks: int, nblocks: int, bpc: int, O=None, q8=None, s8=None, sum8=None,
+                 nb: int = 1, stream=None) -> None:
+    """attn::attn_combine<<<dim3(4, 16, nb), 256>>>(...) (engine/attn.cu:319)."""
+    _check(lib().llattn_attn_combine(_ptr(Opart), _ptr(Mpart), _ptr(Lpart), nchunks, nblocks, bpc, _ptr(O), _ptr(q8),
+                                     _ptr(s8), _ptr(sum8), nb, _stream(stream)))
+
+
+# ------------------------------------------------------------------ batched path
+
+@dataclass
+class Seq:
+    """One sequence of a batched call. `cache` is this layer's [4][head_stride][4736] uint8 tensor, or the record
+    pool when `pages` (int32 [4][head_stride]) is given. Query block j of the sequence sees nblocks + j records."""
+    cache: object
+    nblocks: int
+    nq: int = 1
+    q_first: int = 0
+    pages: object = None
+    head_stride: Optional[int] = None
+
+    def _c(self) -> _Seq:
+        hs = self.head_stride
+        if hs is None:
+            hs = self.pages.shape[-1] if self.pages is not None else (self.cache.shape[1] if self.cache is not None else 0)
+        return _Seq(_ptr(self.cache), _ptr(self.pages), hs, self.nblocks, self.nq, self.q_first)
+
+
+class Context:
+    def __init__(self, device: int = 0):
+        self._h = c_void_p()
+        self.device = device
+        _check(lib().llattn_create(device, byref(self._h)))
+
+    def close(self) -> None:
+        if self._h:
+            lib().llattn_destroy(self._h)
+            self._h = c_void_p()
+
+    def __del__(self):
+        try:
+            self.close()
+        except Exception:
+            pass
+
+    def plan(self, seqs: Sequence[Seq], nctas: int = 0) -> "Plan":
+        return Plan(self, seqs, nctas)
+
+    def attention(self, plan: "Plan", Q, Kf, Vf, O16=None, O32=None, LSE=None, q8=None, s8=None, sum8=None,
+                  scale: float = 0.0, stream=None, parts: int = 3) -> None:
+        """parts: 3 = tile kernel + merge (the normal pass); 1 / 2 run one of the two kernels (per-kernel timing)."""
+        io = _IO(_ptr(Q), _ptr(Kf), _ptr(Vf), _ptr(O16), _ptr(O32), _ptr(LSE), _ptr(q8), _ptr(s8), _ptr(sum8), scale)
+        _check(lib().llattn_attention_parts(self._h, plan._h, byref(io), parts, _stream(stream)))
+
+    def attention_host(self, plan: "Plan", Q, Kf, Vf, O16=None, O32=None, LSE=None, q8=None, s8=None, sum8=None,
+                       scale: float = 0.0, stream=None) -> None:
+        """Q/Kf/Vf and the outputs are HOST tensors (pinned for asynchronous copies)."""
+        io = _IO(_ptr(Q), _ptr(Kf), _ptr(Vf), _ptr(O16), _ptr(O32), _ptr(LSE), _ptr(q8), _ptr(s8), _ptr(sum8), scale)
+        _check(lib().llattn_attention_host(self._h, plan._h, byref(io), _stream(stream)))
+
+    def device_status(self, stream=None) -> int:
+        code = c_int(0)
+        _check(lib().llattn_device_status(self._h, _stream(stream), byref(code)))
+        return code.value
+
+
+class Plan:
+    def __init__(self, ctx: Context, seqs: Sequence[Seq], nctas: int = 0):
+        self.ctx = ctx
+        self._keep = list(seqs)          # keeps the cache / page tensors alive
+        arr = (_Seq * len(seqs))(*[s._c() for s in seqs])
+        self._h = c_void_p()
+        _check(lib().llattn_plan_create(ctx._h, arr, len(seqs), nctas, byref(self._h)))
+        st = PlanStats()
+        _check(lib().llattn_plan_get_stats(self._h, byref(st)))
+        self.stats = st
+
+    def close(self) -> None:
+        if self._h:
+            lib().llattn_plan_destroy(self._h)
+            self._h = c_void_p()
+
+    def __del__(self):
+        try:
+            self.close()
+        except Exception:
+            pass

@@ -1,0 +1,445 @@
+// Block attention over int4 "4c/4" KV records on tcgen05 tensor cores.
+//
+// One CTA per SM walks a list of work items. An item is a run of KV units of one (sequence, query block, kv head):
+// committed records (4736 packed bytes = 32 keys each) and, on the run that ends the context, the query block's own
+// fp16 K/V. The 128 query rows of the kv head (32 tokens x 4 GQA heads) are the M dimension of every MMA.
+// Per tile of up to 4 units (128 keys):
+//   producer warp : cp.async.bulk of whole records global -> shared ring, completion on an mbarrier
+//   dequant warps : nibbles -> fp16 (magic-number unpack, one fp16 FMA per pair as the reference's __hfma2), written
+//                   straight into the no-swizzle UMMA operand layout; fresh fp16 K/V are copied into the same layout
+//   MMA warp      : S = Q K^T  (tcgen05.mma kind::f16, both operands K-major in shared memory, fp32 S in TMEM)
+//                   O += P V   (A = P read from TMEM as packed fp16, B = V MN-major in shared memory, fp32 O in TMEM);
+//                   V carries one extra column of ones, so the same MMA also accumulates the softmax row sum from
+//                   exactly the fp16 P the numerator uses (numerator and denominator then share their rounding)
+//   softmax warps : one thread per query row (TMEM lane); row max, lazy rescale (the reference maximum moves only
+//                   when exceeded by more than 8 in log2 units, engine/attn.cu:237-255), p = 2^(s*scale*log2e - m),
+//                   P stored back over S in TMEM as fp16 pairs
+// The run's un-normalised O (fp32), reference maximum (log2 units) and row sum go to a partial slot in the format of
+// the reference's Opart/Mpart/Lpart (engine/attn.cu:291-305); merge_kernel.cuh folds the slots of a tile together.
+//
+// Operand layout in shared memory (no swizzle): an operand tile is 16 "chunk rows" of CS bytes; chunk row j holds, for
+// each of up to 128 rows (query rows or keys), the 16 bytes of channels 8j..8j+7 at row*16. Within each group of 8
+// channels the order is (0,4,1,5,2,6,3,7): that is what the shift-free nibble unpack produces, Q and the fresh K are
+// stored in the same order (a dot product does not care) and V's order is undone when O is written out.
+// CS = 128*16 + 16: the 16-byte pad makes the 16-byte stores of one warp hit distinct banks.
+//
+// Every wait is bounded (ptx::mbar_wait); a wait that runs out sets a bit in the error word and every role leaves.
+#pragma once
+#include <cuda_fp16.h>
+#include "common.cuh"
+#include "ptx.cuh"
+
+namespace llattn {
+
+constexpr int TILE_UNITS = 4;
+constexpr int CS = 128 * 16 + 16;                  // chunk-row stride, bytes
+constexpr int TILE_BYTES = 16 * CS;                // 33024: Q or K tile
+constexpr int V_ROWS = 18;                         // 16 chunk rows of dims + one holding the ones column + one of zeros
+constexpr int VTILE_BYTES = V_ROWS * CS;           // 37152
+constexpr int PV_N = 144;                          // dims 0..127, column 128 = row sum, 129..143 unused
+constexpr int NRAW = 6;                            // records in flight
+constexpr int RAW_STRIDE = 4864;                   // 4736 rounded up to a multiple of 128
+constexpr int SM_Q = 0;
+constexpr int SM_K = SM_Q + TILE_BYTES;            // two K tiles
+constexpr int SM_V = SM_K + 2 * TILE_BYTES;        // two V tiles
+constexpr int SM_RAW = SM_V + 2 * VTILE_BYTES;
+constexpr int SM_BAR = SM_RAW + NRAW * RAW_STRIDE;
+constexpr int SM_MISC = SM_BAR + 256;
+constexpr int ATTN_SMEM_BYTES = SM_MISC + 16;
+constexpr int ATTN_THREADS = 320;                  // warps 0-3 softmax, 4-7 dequant, 8 producer, 9 MMA
+constexpr int TMEM_COLS = 512;
+constexpr int TM_S = 0, TM_O = 256, TM_L = TM_O + 128;   // S buffers at columns 0 and 128, O at 256..383, row sum at 384
+constexpr float RESCALE_SLACK = 8.f;
+
+// barrier indices
+enum { B_RAW_FULL = 0, B_RAW_EMPTY = B_RAW_FULL + NRAW, B_KV_FULL = B_RAW_EMPTY + NRAW, B_PV_DONE = B_KV_FULL + 2,
+       B_S_FULL = B_PV_DONE + 2, B_P_FULL = B_S_FULL + 2, B_Q_FULL = B_P_FULL + 2, B_O_FREE, B_SPARE, B_COUNT };
+static_assert(B_COUNT * 8 <= 256, "barrier area");
+
+struct KParams {
+    const SeqDesc* seqs;           // list mode
+    const WorkItem* items;
+    const int32_t* cta_first;      // [gridDim.x + 1]
+    const half* Q;
+    const half* Kf;
+    const half* Vf;
+    float* Opart;
+    float* Mpart;
+    float* Lpart;
+    float sl2;                     // softmax scale * log2(e)
+    int* err;
+    // reference-grid mode (items == nullptr): CTA i is (kvh = i % 4, chunk = (i / 4) % ref_nchunks, jb = i / (4 * ref_nchunks))
+    SeqDesc ref_seq;
+    int ref_bpc;
+    int ref_nchunks;
+};
+
+__device__ __forceinline__ bool fetch_item(const KParams& p, int idx, WorkItem& w, SeqDesc& s) {
+    if (p.items) {
+        w = p.items[idx];
+        s = p.seqs[w.seq];
+        return true;
+    }
+    const int kvh = idx & 3, chunk = (idx >> 2) % p.ref_nchunks, jb = (idx >> 2) / p.ref_nchunks;
+    s = p.ref_seq;
+    const int nbl = s.nblocks + jb;
+    const int nch = nbl <= 0 ? 1 : (nbl + p.ref_bpc - 1) / p.ref_bpc;
+    if (chunk >= nch) return false;
+    const int b0 = chunk * p.ref_bpc;
+    w.seq = 0; w.qblk = jb; w.kvh = kvh; w.rec_begin = b0;
+    w.rec_count = nbl <= 0 ? 0 : min(p.ref_bpc, nbl - b0);
+    w.fresh = chunk == nch - 1;
+    w.slot = (jb * NKV + kvh) * p.ref_nchunks + chunk;
+    w.pad = 0;
+    return true;
+}
+
+// 8 nibbles of w -> 4 half2 holding channels (0,4) (1,5) (2,6) (3,7), each value the nibble exactly.
+// Low nibbles of a 16-bit half land in the mantissa of 1024 (0x6400), nibbles at bits 4-7 in the mantissa of 64
+// (0x5400, whose ulp is 1/16); subtracting the bias leaves the integer.
+__device__ __forceinline__ void unpack8(uint32_t w, half2 (&h)[4]) {
+    const uint32_t w8 = w >> 8;
+    uint32_t x0, x1, x2, x3;
+    asm("lop3.b32 %0, %1, %2, %3, 0xea;" : "=r"(x0) : "r"(w), "r"(0x000f000fu), "r"(0x64006400u));
+    asm("lop3.b32 %0, %1, %2, %3, 0xea;" : "=r"(x1) : "r"(w), "r"(0x00f000f0u), "r"(0x54005400u));
+    asm("lop3.b32 %0, %1, %2, %3, 0xea;" : "=r"(x2) : "r"(w8), "r"(0x000f000fu), "r"(0x64006400u));
+    asm("lop3.b32 %0, %1, %2, %3, 0xea;" : "=r"(x3) : "r"(w8), "r"(0x00f000f0u), "r"(0x54005400u));
+    const half2 b1024 = __half2half2(__ushort_as_half(0x6400)), b64 = __half2half2(__ushort_as_half(0x5400));
+    h[0] = __hsub2(*reinterpret_cast<half2*>(&x0), b1024);
+    h[1] = __hsub2(*reinterpret_cast<half2*>(&x1), b64);
+    h[2] = __hsub2(*reinterpret_cast<half2*>(&x2), b1024);
+    h[3] = __hsub2(*reinterpret_cast<half2*>(&x3), b64);
+}
+
+// 8 fp16 in channel order (uint4) -> the (0,4,1,5,2,6,3,7) order.
+__device__ __forceinline__ uint4 permute8(uint4 v) {
+    uint4 o;
+    o.x = __byte_perm(v.x, v.z, 0x5410);
+    o.y = __byte_perm(v.x, v.z, 0x7632);
+    o.z = __byte_perm(v.y, v.w, 0x5410);
+    o.w = __byte_perm(v.y, v.w, 0x7632);
+    return o;
+}
+
+__device__ __forceinline__ float ex2(float x) {
+    float y;
+    asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+    return y;
+}
+
+// One staged record -> fp16 K and V at key offset (unit * 32) of a tile pair. dt = 0..127.
+__device__ __forceinline__ void dequant_record(const uint8_t* raw, uint8_t* Kt, uint8_t* Vt, int dt) {
+    const int c = dt & 15, tb = dt >> 4;
+    const uint4 s4 = permute8(*reinterpret_cast<const uint4*>(raw + KOFF_META + c * 16));
+    const uint4 m4 = permute8(*reinterpret_cast<const uint4*>(raw + KOFF_META + 256 + c * 16));
+    const half2* ks = reinterpret_cast<const half2*>(&s4);
+    const half2* km = reinterpret_cast<const half2*>(&m4);
+    const half* vmeta = reinterpret_cast<const half*>(raw + VOFF_META);
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+        const int tok = tb + 8 * i;
+        const uint32_t kw = *reinterpret_cast<const uint32_t*>(raw + tok * 64 + c * 4);
+        const uint32_t vw = *reinterpret_cast<const uint32_t*>(raw + VOFF + tok * 64 + c * 4);
+        const half2 vs = __half2half2(vmeta[tok]), vm = __half2half2(vmeta[BLK + tok]);
+        half2 kh[4], vh[4];
+        unpack8(kw, kh);
+        unpack8(vw, vh);
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+            kh[j] = __hfma2(kh[j], ks[j], km[j]);
+            vh[j] = __hfma2(vh[j], vs, vm);
+        }
+        *reinterpret_cast<uint4*>(Kt + c * CS + tok * 16) = *reinterpret_cast<const uint4*>(kh);
+        *reinterpret_cast<uint4*>(Vt + c * CS + tok * 16) = *reinterpret_cast<const uint4*>(vh);
+    }
+}
+
+__global__ void __launch_bounds__(ATTN_THREADS, 1) attn_tile_kernel(const __grid_constant__ KParams p) {
+    extern __shared__ __align__(128) uint8_t smem[];
+    uint64_t* bars = reinterpret_cast<uint64_t*>(smem + SM_BAR);
+    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(smem + SM_MISC);
+    volatile int* abort_flag = reinterpret_cast<volatile int*>(smem + SM_MISC + 4);
+    const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+    const uint32_t bar0 = ptx::smem_u32(bars);
+    auto BAR = [&](int i) -> uint32_t { return bar0 + 8u * uint32_t(i); };
+
+    int i0, i1;
+    if (p.items) { i0 = p.cta_first[blockIdx.x]; i1 = p.cta_first[blockIdx.x + 1]; }
+    else { i0 = blockIdx.x; i1 = blockIdx.x + 1; }
+
+    if (tid == 0) {
+        for (int i = 0; i < NRAW; ++i) { ptx::mbar_init(BAR(B_RAW_FULL + i), 1); ptx::mbar_init(BAR(B_RAW_EMPTY + i), 128); }
+        for (int i = 0; i < 2; ++i) {
+            ptx::mbar_init(BAR(B_KV_FULL + i), 128); ptx::mbar_init(BAR(B_PV_DONE + i), 1);
+            ptx::mbar_init(BAR(B_S_FULL + i), 1); ptx::mbar_init(BAR(B_P_FULL + i), 128);
+        }
+        ptx::mbar_init(BAR(B_Q_FULL), 128); ptx::mbar_init(BAR(B_O_FREE), 128); ptx::mbar_init(BAR(B_SPARE), 1);
+        ptx::fence_mbar_init();
+        *abort_flag = 0;
+    }
+    if (warp == 9) { ptx::tmem_alloc(ptx::smem_u32(tmem_slot), TMEM_COLS); ptx::tmem_relinquish(); }
+    ptx::tc_fence_before();
+    __syncthreads();
+    ptx::tc_fence_after();
+    const uint32_t tmem = *tmem_slot;
+    int errbits = 0;
+
+    if (warp < 4) {
+        // ================================================================== softmax + epilogue: thread = query row
+        const uint32_t tlane = tmem + (uint32_t(warp * 32) << 16);
+        uint32_t t = 0;
+        bool alive = true;
+#pragma unroll 1
+        for (int ii = i0; ii < i1 && alive; ++ii) {
+            WorkItem w; SeqDesc s;
+            if (!fetch_item(p, ii, w, s)) continue;
+            const int U = w.rec_count + w.fresh, ntiles = (U + TILE_UNITS - 1) / TILE_UNITS;
+            float mref = -INFINITY;
+#pragma unroll 1
+            for (int i = 0; i < ntiles; ++i, ++t) {
+                const int b = t & 1, nu = min(TILE_UNITS, U - TILE_UNITS * i);
+                if (!ptx::mbar_wait(BAR(B_S_FULL + b), (t >> 1) & 1, abort_flag)) { alive = false; errbits |= ERR_WAIT_SOFTMAX; break; }
+                ptx::tc_fence_after();
+                const uint32_t ts = tlane + TM_S + b * 128;
+                float mx = -INFINITY;
+#pragma unroll 1
+                for (int c = 0; c < nu; ++c) {
+                    uint32_t r[32];
+                    ptx::tmem_ld32(ts + 32 * c, r);
+                    ptx::tmem_wait_ld();
+#pragma unroll
+                    for (int j = 0; j < 32; ++j) mx = fmaxf(mx, __uint_as_float(r[j]));
+                }
+                const float msc = mx * p.sl2;
+                const bool moved = msc > mref + RESCALE_SLACK;
+                if (i > 0 && __any_sync(0xffffffffu, moved)) {
+                    // the accumulated O of this row group is rescaled to the new reference maximum; every PV issued
+                    // so far must have landed first
+                    if (!ptx::mbar_wait(BAR(B_PV_DONE + (b ^ 1)), ((t - 1) >> 1) & 1, abort_flag)) { alive = false; errbits |= ERR_WAIT_SOFTMAX; break; }
+                    ptx::tc_fence_after();
+                    const float corr = moved ? ex2(mref - msc) : 1.f;
+#pragma unroll 1
+                    for (int c = 0; c < 4; ++c) {
+                        uint32_t r[32];
+                        ptx::tmem_ld32(tlane + TM_O + 32 * c, r);
+                        ptx::tmem_wait_ld();
+#pragma unroll
+                        for (int j = 0; j < 32; ++j) r[j] = __float_as_uint(__uint_as_float(r[j]) * corr);
+                        ptx::tmem_st32(tlane + TM_O + 32 * c, r);
+                    }
+                    {
+                        uint32_t r[16];
+                        ptx::tmem_ld16(tlane + TM_L, r);
+                        ptx::tmem_wait_ld();
+                        r[0] = __float_as_uint(__uint_as_float(r[0]) * corr);
+                        ptx::tmem_st16(tlane + TM_L, r);
+                    }
+                    ptx::tmem_wait_st();
+                }
+                if (moved) mref = msc;
+#pragma unroll 1
+                for (int c = 0; c < nu; ++c) {
+                    uint32_t r[32], pk[16];
+                    ptx::tmem_ld32(ts + 32 * c, r);
+                    ptx::tmem_wait_ld();
+#pragma unroll
+                    for (int j = 0; j < 16; ++j) {
+                        const float p0 = ex2(fmaf(__uint_as_float(r[2 * j]), p.sl2, -mref));
+                        const float p1 = ex2(fmaf(__uint_as_float(r[2 * j + 1]), p.sl2, -mref));
+                        const half2 h = __floats2half2_rn(p0, p1);
+                        pk[j] = *reinterpret_cast<const uint32_t*>(&h);
+                    }
+                    ptx::tmem_st16(ts + 16 * c, pk);
+                }
+                ptx::tmem_wait_st();
+                ptx::tc_fence_before();
+                ptx::mbar_arrive(BAR(B_P_FULL + b));
+            }
+            if (!alive) break;
+            // ---- epilogue: un-normalised O, reference maximum and row sum of this run
+            const uint32_t tl = t - 1;
+            if (!ptx::mbar_wait(BAR(B_PV_DONE + (tl & 1)), (tl >> 1) & 1, abort_flag)) { alive = false; errbits |= ERR_WAIT_SOFTMAX; break; }
+            ptx::tc_fence_after();
+            float* orow = p.Opart + (size_t(w.slot) * QR + tid) * D;
+#pragma unroll 1
+            for (int c = 0; c < 4; ++c) {
+                uint32_t r[32];
+                ptx::tmem_ld32(tlane + TM_O + 32 * c, r);
+                ptx::tmem_wait_ld();
+#pragma unroll
+                for (int g = 0; g < 4; ++g) {      // positions (0..7) hold dims (0,4,1,5,2,6,3,7)
+                    const float4 lo = make_float4(__uint_as_float(r[8 * g]), __uint_as_float(r[8 * g + 2]),
+                                                  __uint_as_float(r[8 * g + 4]), __uint_as_float(r[8 * g + 6]));
+                    const float4 hi = make_float4(__uint_as_float(r[8 * g + 1]), __uint_as_float(r[8 * g + 3]),
+                                                  __uint_as_float(r[8 * g + 5]), __uint_as_float(r[8 * g + 7]));
+                    *reinterpret_cast<float4*>(orow + 32 * c + 8 * g) = lo;
+                    *reinterpret_cast<float4*>(orow + 32 * c + 8 * g + 4) = hi;
+                }
+            }
+            {
+                uint32_t r[16];
+                ptx::tmem_ld16(tlane + TM_L, r);
+                ptx::tmem_wait_ld();
+                p.Lpart[size_t(w.slot) * QR + tid] = __uint_as_float(r[0]);
+            }
+            p.Mpart[size_t(w.slot) * QR + tid] = mref;
+            ptx::tc_fence_before();
+            ptx::mbar_arrive(BAR(B_O_FREE));
+        }
+    } else if (warp < 8) {
+        // ================================================================== dequant: records -> fp16 operand tiles
+        const int dt = tid - 128;
+        uint32_t t = 0, r = 0;
+        int prev_last = -1;
+        bool alive = true;
+        // chunk row 16 of both V tiles: (1, 0, 0, 0, 0, 0, 0, 0) for every key -> O column 128 accumulates sum(P);
+        // chunk row 17: zeros. Published by the first kv_full arrival.
+        for (int idx = dt; idx < 2 * 2 * 128; idx += 128) {
+            const int buf = idx >> 8, row = (idx >> 7) & 1, key = idx & 127;
+            *reinterpret_cast<uint4*>(smem + SM_V + buf * VTILE_BYTES + (16 + row) * CS + key * 16) =
+                make_uint4(row == 0 ? 0x00003C00u : 0u, 0u, 0u, 0u);
+        }
+#pragma unroll 1
+        for (int ii = i0; ii < i1 && alive; ++ii) {
+            WorkItem w; SeqDesc s;
+            if (!fetch_item(p, ii, w, s)) continue;
+            const int U = w.rec_count + w.fresh, ntiles = (U + TILE_UNITS - 1) / TILE_UNITS;
+            const size_t qg = size_t(s.q_first + w.qblk);
+            if (prev_last >= 0 &&      // Q is overwritten: every MMA of the previous item must be done
+                !ptx::mbar_wait(BAR(B_PV_DONE + (prev_last & 1)), (uint32_t(prev_last) >> 1) & 1, abort_flag)) { alive = false; errbits |= ERR_WAIT_DEQUANT; break; }
+#pragma unroll 4
+            for (int i = 0; i < 16; ++i) {
+                const int idx = dt + 128 * i, row = idx >> 4, ch = idx & 15;
+                const half* src = p.Q + ((qg * BLK + (row >> 2)) * NQH + 4 * w.kvh + (row & 3)) * D + ch * 8;
+                *reinterpret_cast<uint4*>(smem + SM_Q + ch * CS + row * 16) = permute8(__ldg(reinterpret_cast<const uint4*>(src)));
+            }
+            ptx::fence_proxy_async_smem();
+            ptx::mbar_arrive(BAR(B_Q_FULL));
+#pragma unroll 1
+            for (int i = 0; i < ntiles && alive; ++i, ++t) {
+                const int b = t & 1, nu = min(TILE_UNITS, U - TILE_UNITS * i);
+                if (t >= 2 && !ptx::mbar_wait(BAR(B_PV_DONE + b), ((t >> 1) - 1) & 1, abort_flag)) { alive = false; errbits |= ERR_WAIT_DEQUANT; break; }
+                uint8_t* Kt = smem + SM_K + b * TILE_BYTES;
+                uint8_t* Vt = smem + SM_V + b * VTILE_BYTES;
+#pragma unroll 1
+                for (int u = 0; u < nu; ++u) {
+                    const int unit = TILE_UNITS * i + u;
+                    if (unit < w.rec_count) {
+                        const uint32_t slot = r % NRAW;
+                        if (!ptx::mbar_wait(BAR(B_RAW_FULL + slot), (r / NRAW) & 1, abort_flag)) { alive = false; errbits |= ERR_WAIT_DEQUANT; break; }
+                        dequant_record(smem + SM_RAW + slot * RAW_STRIDE, Kt + u * 512, Vt + u * 512, dt);
+                        ptx::mbar_arrive(BAR(B_RAW_EMPTY + slot));
+                        ++r;
+                    } else {          // the query block's own K/V, exact fp16
+                        const size_t f0 = (qg * BLK) * NKV * D + size_t(w.kvh) * D;
+#pragma unroll
+                        for (int k = 0; k < 4; ++k) {
+                            const int idx = dt + 128 * k, tok = idx >> 4, ch = idx & 15;
+                            const size_t off = f0 + size_t(tok) * NKV * D + ch * 8;
+                            *reinterpret_cast<uint4*>(Kt + u * 512 + ch * CS + tok * 16) = permute8(__ldg(reinterpret_cast<const uint4*>(p.Kf + off)));
+                            *reinterpret_cast<uint4*>(Vt + u * 512 + ch * CS + tok * 16) = permute8(__ldg(reinterpret_cast<const uint4*>(p.Vf + off)));
+                        }
+                    }
+                }
+                if (!alive) break;
+                ptx::fence_proxy_async_smem();
+                ptx::mbar_arrive(BAR(B_KV_FULL + b));
+            }
+            prev_last = int(t) - 1;
+        }
+    } else if (warp == 8) {
+        // ================================================================== producer: bulk copies of records
+        uint32_t r = 0;
+        bool alive = true;
+#pragma unroll 1
+        for (int ii = i0; ii < i1 && alive; ++ii) {
+            WorkItem w; SeqDesc s;
+            if (!fetch_item(p, ii, w, s)) continue;
+            const size_t hbase = size_t(w.kvh) * s.head_stride;
+#pragma unroll 1
+            for (int u = 0; u < w.rec_count; ++u, ++r) {
+                const uint32_t slot = r % NRAW;
+                if (r >= NRAW && !ptx::mbar_wait(BAR(B_RAW_EMPTY + slot), ((r / NRAW) - 1) & 1, abort_flag)) { alive = false; errbits |= ERR_WAIT_PRODUCER; break; }
+                if (lane == 0) {
+                    const size_t ridx = s.pages ? size_t(s.pages[hbase + w.rec_begin + u]) : hbase + w.rec_begin + u;
+                    ptx::mbar_arrive_expect_tx(BAR(B_RAW_FULL + slot), REC_BYTES);
+                    ptx::bulk_g2s(ptx::smem_u32(smem + SM_RAW + slot * RAW_STRIDE), s.cache + ridx * REC_BYTES, REC_BYTES,
+                                  BAR(B_RAW_FULL + slot));
+                }
+                __syncwarp();
+            }
+        }
+        // copies still in flight must land before the shared memory is given back
+        if (*abort_flag) {
+            const uint32_t n = r < NRAW ? r : NRAW;
+            for (uint32_t k = 0; k < n; ++k) {
+                const uint32_t rr = r - 1 - k;
+                volatile int never = 0;
+                ptx::mbar_wait(BAR(B_RAW_FULL + rr % NRAW), (rr / NRAW) & 1, &never);
+            }
+        }
+    } else {
+        // ================================================================== MMA issue (lane 0 issues, the warp stays together)
+        uint32_t t = 0, itc = 0;
+        bool alive = true;
+        const uint32_t q_s = ptx::smem_u32(smem + SM_Q), k_s = ptx::smem_u32(smem + SM_K), v_s = ptx::smem_u32(smem + SM_V);
+        const uint32_t idO = ptx::idesc_f16(128, PV_N, false, true);
+        auto issue_pv = [&](uint32_t tt, int nu, bool first) -> bool {
+            const uint32_t bb = tt & 1;
+            if (!ptx::mbar_wait(BAR(B_P_FULL + bb), (tt >> 1) & 1, abort_flag)) return false;
+            if (first && itc > 0 && !ptx::mbar_wait(BAR(B_O_FREE), (itc - 1) & 1, abort_flag)) return false;
+            ptx::tc_fence_after();
+            if (lane == 0) {
+                for (int j = 0; j < 2 * nu; ++j)   // 16 keys per step: B is MN-major, 8-key groups 128 B apart, dim groups CS apart
+                    ptx::mma_ts(tmem + TM_O, tmem + TM_S + bb * 128 + j * 8,
+                                ptx::smem_desc(v_s + bb * VTILE_BYTES + j * 256, 128, CS), idO, (first && j == 0) ? 0u : 1u);
+                ptx::mma_commit(BAR(B_PV_DONE + bb));
+            }
+            __syncwarp();
+            return true;
+        };
+#pragma unroll 1
+        for (int ii = i0; ii < i1 && alive; ++ii) {
+            WorkItem w; SeqDesc s;
+            if (!fetch_item(p, ii, w, s)) continue;
+            const int U = w.rec_count + w.fresh, ntiles = (U + TILE_UNITS - 1) / TILE_UNITS;
+            if (!ptx::mbar_wait(BAR(B_Q_FULL), itc & 1, abort_flag)) { alive = false; errbits |= ERR_WAIT_MMA; break; }
+            int nu_prev = 0;
+#pragma unroll 1
+            for (int i = 0; i < ntiles; ++i, ++t) {
+                const uint32_t b = t & 1;
+                const int nu = min(TILE_UNITS, U - TILE_UNITS * i);
+                if (!ptx::mbar_wait(BAR(B_KV_FULL + b), (t >> 1) & 1, abort_flag)) { alive = false; errbits |= ERR_WAIT_MMA; break; }
+                ptx::tc_fence_after();
+                if (lane == 0) {
+                    const uint32_t idS = ptx::idesc_f16(128, 32 * nu, false, false);
+#pragma unroll
+                    for (int j = 0; j < 8; ++j)    // 16 channels per step: both operands K-major, chunk rows CS apart, 8-row groups 128 B apart
+                        ptx::mma_ss(tmem + TM_S + b * 128, ptx::smem_desc(q_s + 2 * j * CS, CS, 128),
+                                    ptx::smem_desc(k_s + b * TILE_BYTES + 2 * j * CS, CS, 128), idS, j > 0 ? 1u : 0u);
+                    ptx::mma_commit(BAR(B_S_FULL + b));
+                }
+                __syncwarp();
+                if (i > 0 && !issue_pv(t - 1, nu_prev, i == 1)) { alive = false; errbits |= ERR_WAIT_MMA; break; }
+                nu_prev = nu;
+            }
+            if (!alive) break;
+            if (!issue_pv(t - 1, nu_prev, ntiles == 1)) { alive = false; errbits |= ERR_WAIT_MMA; break; }
+            ++itc;
+        }
+        // every MMA issued must have retired before tensor memory is released
+        if (lane == 0) ptx::mma_commit(BAR(B_SPARE));
+        __syncwarp();
+        {
+            volatile int never = 0;
+            if (!ptx::mbar_wait(BAR(B_SPARE), 0, &never)) errbits |= ERR_WAIT_TEARDOWN;
+        }
+    }
+
+    if (errbits && p.err) atomicOr(p.err, errbits);
+    ptx::tc_fence_before();
+    __syncthreads();
+    if (warp == 9) ptx::tmem_dealloc(tmem, TMEM_COLS);
+}
+
+}  // namespace llattn

@@ -1,0 +1,319 @@
+// Attention entry points of the C ABI (included at the end of llattn.cu): the reference-shaped operator pair, the
+// context, the host-side work planner and the batched launches.
+
+namespace {
+
+constexpr size_t SLOT_O_BYTES = size_t(llattn::QR) * llattn::D * sizeof(float);   // 64 KiB
+constexpr size_t SLOT_ML_BYTES = size_t(llattn::QR) * sizeof(float);
+
+// Splits the flattened unit sequence (every (sequence, query block, kv head) tile contributes nblocks + j records and
+// one fresh block, in that order) into `nctas` contiguous shares of near-equal size. A share boundary inside a tile
+// falls on a multiple of 4 units from the tile's start so that 128-key MMA tiles stay full, and a run is never
+// shorter than `min_units` unless the tile itself is. Every run gets its own partial slot; the slots of one tile are
+// consecutive.
+struct HostPlan {
+    std::vector<llattn::SeqDesc> seqs;
+    std::vector<llattn::WorkItem> items;
+    std::vector<int32_t> cta_first;
+    std::vector<llattn::MergeDesc> merge;
+    int64_t total_units = 0, max_cta_units = 0;
+    int nq_total = 0;
+};
+
+int build_plan(const llattn_seq* seqs, int nseq, int nctas, HostPlan& hp) {
+    using namespace llattn;
+    hp.seqs.resize(nseq);
+    int64_t total = 0;
+    int nq_total = 0;
+    for (int s = 0; s < nseq; ++s) {
+        const llattn_seq& q = seqs[s];
+        if (!q.cache && q.nblocks + q.nq - 1 > 0) return fail(LLATTN_EINVAL, "plan: sequence %d has a null cache", s);
+        if (q.nblocks < 0 || q.nq < 1 || q.q_first < 0 || q.head_stride < 0)
+            return fail(LLATTN_EINVAL, "plan: sequence %d has a negative count (nblocks %d, nq %d, q_first %d)", s, q.nblocks, q.nq, q.q_first);
+        if (q.nblocks + q.nq - 1 > q.head_stride)
+            return fail(LLATTN_EINVAL, "plan: sequence %d reads %d blocks but head_stride is %d", s, q.nblocks + q.nq - 1, q.head_stride);
+        if (q.cache && !aligned16(q.cache)) return fail(LLATTN_EINVAL, "plan: sequence %d cache is not 16-byte aligned", s);
+        hp.seqs[s] = SeqDesc{static_cast<const uint8_t*>(q.cache), q.pages, q.head_stride, q.nblocks, q.nq, q.q_first};
+        for (int j = 0; j < q.nq; ++j) total += int64_t(NKV) * (q.nblocks + j + 1);
+        nq_total = std::max(nq_total, q.q_first + q.nq);
+    }
+    hp.total_units = total;
+    hp.nq_total = nq_total;
+    constexpr int64_t MIN_UNITS = 16;
+    int64_t share = (total + nctas - 1) / nctas;
+    share = std::max<int64_t>(share, MIN_UNITS);
+    share = (share + TILE_UNITS - 1) / TILE_UNITS * TILE_UNITS;
+    hp.cta_first.assign(1, 0);
+    int64_t room = share;      // units the current CTA can still take
+    int slot = 0;
+    auto next_cta = [&]() { hp.cta_first.push_back(int32_t(hp.items.size())); room = share; };
+    for (int s = 0; s < nseq; ++s)
+        for (int j = 0; j < seqs[s].nq; ++j)
+            for (int h = 0; h < NKV; ++h) {
+                const int nrec = seqs[s].nblocks + j;
+                const int U = nrec + 1;
+                int done = 0;
+                const int slot0 = slot;
+                while (done < U) {
+                    int take = int(std::min<int64_t>(room, U - done));
+                    if (take < U - done) take = take / TILE_UNITS * TILE_UNITS;     // keep the cut on a tile boundary
+                    if (take == 0) { next_cta(); continue; }
+                    const int rec_cnt = std::min(take, nrec - done);
+                    hp.items.push_back(WorkItem{s, j, h, done, std::max(rec_cnt, 0), done + take == U ? 1 : 0, slot++, 0});
+                    done += take;
+                    room -= take;
+                    if (room <= 0) next_cta();
+                }
+                hp.merge.push_back(MergeDesc{seqs[s].q_first + j, h, slot0, slot - slot0});
+            }
+    if (hp.cta_first.back() != int32_t(hp.items.size())) hp.cta_first.push_back(int32_t(hp.items.size()));
+    hp.max_cta_units = 0;
+    for (size_t c = 0; c + 1 < hp.cta_first.size(); ++c) {
+        int64_t u = 0;
+        for (int i = hp.cta_first[c]; i < hp.cta_first[c + 1]; ++i) u += hp.items[i].rec_count + hp.items[i].fresh;
+        hp.max_cta_units = std::max(hp.max_cta_units, u);
+    }
+    return LLATTN_OK;
+}
+
+int check_io(const llattn_io* io, const char* who) {
+    if (!io || !io->Q || !io->Kf || !io->Vf) return fail(LLATTN_EINVAL, "%s: Q, Kf and Vf are required", who);
+    if (!io->O16 && !io->O32 && !io->q8 && !io->LSE) return fail(LLATTN_EINVAL, "%s: no output requested", who);
+    if (io->q8 && (!io->s8 || !io->sum8)) return fail(LLATTN_EINVAL, "%s: q8 needs s8 and sum8", who);
+    return LLATTN_OK;
+}
+
+}  // namespace
+
+extern "C" {
+
+// ----------------------------------------------------------------------------- the reference operator pair
+
+int llattn_attn_partial(const llattn_args* a, int nb, int* err_word, void* stream) {
+    using namespace llattn;
+    if (!a || !a->Q || !a->Kf || !a->Vf || !a->Opart || !a->Mpart || !a->Lpart) return fail(LLATTN_EINVAL, "attn_partial: null pointer");
+    if (nb < 1 || a->nblocks < 0 || a->blocks_per_chunk < 1 || a->nchunks < 1)
+        return fail(LLATTN_EINVAL, "attn_partial: bad shape (nb %d, nblocks %d, bpc %d, nchunks %d)", nb, a->nblocks, a->blocks_per_chunk, a->nchunks);
+    if (a->nblocks + nb - 1 > 0 && !a->cache) return fail(LLATTN_EINVAL, "attn_partial: null cache with committed blocks");
+    if (a->nblocks + nb - 1 > a->max_blocks) return fail(LLATTN_EINVAL, "attn_partial: %d blocks visible, cache holds %d", a->nblocks + nb - 1, a->max_blocks);
+    if (llattn_chunks_for(a->nblocks + nb - 1, a->blocks_per_chunk) > a->nchunks)
+        return fail(LLATTN_EINVAL, "attn_partial: %d chunks needed, %d slots given", llattn_chunks_for(a->nblocks + nb - 1, a->blocks_per_chunk), a->nchunks);
+    if (!aligned16(a->Q) || !aligned16(a->Kf) || !aligned16(a->Vf) || !aligned16(a->cache) || !aligned16(a->Opart))
+        return fail(LLATTN_EINVAL, "attn_partial: pointers must be 16-byte aligned");
+    if (int rc = ensure_kernel_attrs()) return rc;
+    KParams p{};
+    p.Q = static_cast<const half*>(a->Q); p.Kf = static_cast<const half*>(a->Kf); p.Vf = static_cast<const half*>(a->Vf);
+    p.Opart = a->Opart; p.Mpart = a->Mpart; p.Lpart = a->Lpart;
+    p.sl2 = a->scale * 1.4426950408889634f;
+    p.err = err_word;
+    p.ref_seq = SeqDesc{static_cast<const uint8_t*>(a->cache), nullptr, a->max_blocks, a->nblocks, nb, 0};
+    p.ref_bpc = a->blocks_per_chunk;
+    p.ref_nchunks = a->nchunks;
+    attn_tile_kernel<<<NKV * a->nchunks * nb, ATTN_THREADS, ATTN_SMEM_BYTES, as_stream(stream)>>>(p);
+    CU(cudaGetLastError());
+    return LLATTN_OK;
+}
+
+int llattn_attn_combine(const float* Opart, const float* Mpart, const float* Lpart, int nchunks, int nblocks, int bpc,
+                        void* O, int8_t* q8, float* s8, int32_t* sum8, int nb, void* stream) {
+    using namespace llattn;
+    if (!Opart || !Mpart || !Lpart) return fail(LLATTN_EINVAL, "attn_combine: null partial buffer");
+    if (!O && !q8) return fail(LLATTN_EINVAL, "attn_combine: neither O nor q8 given");
+    if (q8 && (!s8 || !sum8)) return fail(LLATTN_EINVAL, "attn_combine: q8 needs s8 and sum8");
+    if (nb < 1 || nchunks < 1 || bpc < 1 || nblocks < 0) return fail(LLATTN_EINVAL, "attn_combine: bad shape");
+    MergeOut o{};
+    if (q8) { o.q8 = q8; o.s8 = s8; o.sum8 = sum8; }       // as the reference: int8 form replaces the fp16 output
+    else o.O16 = static_cast<half*>(O);
+    combine_ref_kernel<<<dim3(NKV, QR / MERGE_ROWS, nb), MERGE_THREADS, 0, as_stream(stream)>>>(Opart, Mpart, Lpart, nchunks, nblocks, bpc, o);
+    CU(cudaGetLastError());
+    return LLATTN_OK;
+}
+
+// ----------------------------------------------------------------------------- context
+
+int llattn_create(int device, llattn_ctx** out) {
+    if (!out) return fail(LLATTN_EINVAL, "create: null out pointer");
+    *out = nullptr;
+    int ndev = 0;
+    CU(cudaGetDeviceCount(&ndev));
+    if (device < 0 || device >= ndev) return fail(LLATTN_EINVAL, "create: device %d of %d", device, ndev);
+    DeviceGuard g(device);
+    if (!g.ok) return fail(LLATTN_ECUDA, "create: cannot select device %d", device);
+    cudaDeviceProp prop;
+    CU(cudaGetDeviceProperties(&prop, device));
+    if (prop.major != 10) return fail(LLATTN_ECUDA, "create: device %d is sm_%d%d; this library holds sm_100a code only", device, prop.major, prop.minor);
+    llattn_ctx* c = new (std::nothrow) llattn_ctx();
+    if (!c) return fail(LLATTN_ENOMEM, "create: out of host memory");
+    c->device = device;
+    c->num_sms = prop.multiProcessorCount;
+    if (cudaMalloc(&c->err_word, sizeof(int)) != cudaSuccess || cudaMemset(c->err_word, 0, sizeof(int)) != cudaSuccess) {
+        cudaGetLastError();
+        delete c;
+        return fail(LLATTN_ENOMEM, "create: cannot allocate the device error word");
+    }
+    if (int rc = ensure_kernel_attrs()) { cudaFree(c->err_word); delete c; return rc; }
+    *out = c;
+    return LLATTN_OK;
+}
+
+void llattn_destroy(llattn_ctx* c) {
+    if (!c) return;
+    DeviceGuard g(c->device);
+    cudaFree(c->err_word);
+    cudaFree(c->workspace);
+    cudaFree(c->stage);
+    delete c;
+}
+
+int llattn_plan_create(llattn_ctx* c, const llattn_seq* seqs, int nseq, int nctas, llattn_plan** out) {
+    using namespace llattn;
+    if (!c || !seqs || !out) return fail(LLATTN_EINVAL, "plan_create: null pointer");
+    *out = nullptr;
+    if (nseq < 1) return fail(LLATTN_EINVAL, "plan_create: nseq must be positive");
+    if (nctas <= 0) nctas = c->num_sms;
+    HostPlan hp;
+    if (int rc = build_plan(seqs, nseq, nctas, hp)) return rc;
+    std::lock_guard<std::mutex> lk(c->mu);
+    DeviceGuard g(c->device);
+    if (!g.ok) return fail(LLATTN_ECUDA, "plan_create: cannot select device %d", c->device);
+    llattn_plan* pl = new (std::nothrow) llattn_plan();
+    if (!pl) return fail(LLATTN_ENOMEM, "plan_create: out of host memory");
+    pl->ctx = c;
+    auto up = [](size_t x) { return (x + 255) / 256 * 256; };
+    const size_t b_seq = up(hp.seqs.size() * sizeof(SeqDesc)), b_it = up(hp.items.size() * sizeof(WorkItem)),
+                 b_cf = up(hp.cta_first.size() * sizeof(int32_t)), b_md = up(hp.merge.size() * sizeof(MergeDesc));
+    std::vector<uint8_t> blob(b_seq + b_it + b_cf + b_md, 0);
+    memcpy(blob.data(), hp.seqs.data(), hp.seqs.size() * sizeof(SeqDesc));
+    memcpy(blob.data() + b_seq, hp.items.data(), hp.items.size() * sizeof(WorkItem));
+    memcpy(blob.data() + b_seq + b_it, hp.cta_first.data(), hp.cta_first.size() * sizeof(int32_t));
+    memcpy(blob.data() + b_seq + b_it + b_cf, hp.merge.data(), hp.merge.size() * sizeof(MergeDesc));
+    if (cudaMalloc(&pl->dev_blob, blob.size()) != cudaSuccess) { cudaGetLastError(); delete pl; return fail(LLATTN_ENOMEM, "plan_create: cudaMalloc of %zu bytes failed", blob.size()); }
+    if (cudaMemcpy(pl->dev_blob, blob.data(), blob.size(), cudaMemcpyHostToDevice) != cudaSuccess) {
+        cudaGetLastError(); cudaFree(pl->dev_blob); delete pl;
+        return fail(LLATTN_ECUDA, "plan_create: upload failed");
+    }
+    const uint8_t* d = static_cast<const uint8_t*>(pl->dev_blob);
+    pl->d_seqs = reinterpret_cast<const SeqDesc*>(d);
+    pl->d_items = reinterpret_cast<const WorkItem*>(d + b_seq);
+    pl->d_cta_first = reinterpret_cast<const int32_t*>(d + b_seq + b_it);
+    pl->d_merge = reinterpret_cast<const MergeDesc*>(d + b_seq + b_it + b_cf);
+    pl->ntiles_out = int(hp.merge.size());
+    pl->stats.nseq = nseq;
+    pl->stats.nq_total = hp.nq_total;
+    pl->stats.nitems = int32_t(hp.items.size());
+    pl->stats.nslots = int32_t(hp.items.size());
+    pl->stats.nctas = int32_t(hp.cta_first.size()) - 1;
+    pl->stats.total_units = hp.total_units;
+    pl->stats.max_cta_units = hp.max_cta_units;
+    pl->stats.workspace_bytes = hp.items.size() * (SLOT_O_BYTES + 2 * SLOT_ML_BYTES);
+    if (int rc = grow(&c->workspace, &c->workspace_bytes, pl->stats.workspace_bytes)) { cudaFree(pl->dev_blob); delete pl; return rc; }
+    *out = pl;
+    return LLATTN_OK;
+}
+
+void llattn_plan_destroy(llattn_plan* pl) {
+    if (!pl) return;
+    DeviceGuard g(pl->ctx->device);
+    cudaFree(pl->dev_blob);
+    delete pl;
+}
+
+int llattn_plan_get_stats(const llattn_plan* pl, llattn_plan_stats* out) {
+    if (!pl || !out) return fail(LLATTN_EINVAL, "plan_get_stats: null pointer");
+    *out = pl->stats;
+    return LLATTN_OK;
+}
+
+int llattn_attention(llattn_ctx* c, const llattn_plan* pl, const llattn_io* io, void* stream) {
+    return llattn_attention_parts(c, pl, io, 3, stream);
+}
+
+int llattn_attention_parts(llattn_ctx* c, const llattn_plan* pl, const llattn_io* io, int parts, void* stream) {
+    using namespace llattn;
+    if (!c || !pl || pl->ctx != c) return fail(LLATTN_EINVAL, "attention: plan does not belong to this context");
+    if (parts < 1 || parts > 3) return fail(LLATTN_EINVAL, "attention: parts must be 1, 2 or 3");
+    if (int rc = check_io(io, "attention")) return rc;
+    if (!aligned16(io->Q) || !aligned16(io->Kf) || !aligned16(io->Vf) || !aligned16(io->O16) || !aligned16(io->O32))
+        return fail(LLATTN_EINVAL, "attention: pointers must be 16-byte aligned");
+    if (c->workspace_bytes < pl->stats.workspace_bytes) return fail(LLATTN_ENOMEM, "attention: workspace smaller than the plan needs");
+    int dev = -1;
+    CU(cudaGetDevice(&dev));
+    if (dev != c->device) return fail(LLATTN_EINVAL, "attention: current device %d, context device %d", dev, c->device);
+    const size_t ns = size_t(pl->stats.nslots);
+    float* Opart = static_cast<float*>(c->workspace);
+    float* Mpart = Opart + ns * QR * D;
+    float* Lpart = Mpart + ns * QR;
+    KParams p{};
+    p.seqs = pl->d_seqs; p.items = pl->d_items; p.cta_first = pl->d_cta_first;
+    p.Q = static_cast<const half*>(io->Q); p.Kf = static_cast<const half*>(io->Kf); p.Vf = static_cast<const half*>(io->Vf);
+    p.Opart = Opart; p.Mpart = Mpart; p.Lpart = Lpart;
+    p.sl2 = (io->scale > 0.f ? io->scale : 0.08838834764831845f) * 1.4426950408889634f;
+    p.err = c->err_word;
+    if (parts & 1) {
+        attn_tile_kernel<<<pl->stats.nctas, ATTN_THREADS, ATTN_SMEM_BYTES, as_stream(stream)>>>(p);
+        CU(cudaGetLastError());
+    }
+    if (parts & 2) {
+        MergeOut o{static_cast<half*>(io->O16), io->O32, io->LSE, io->q8, io->s8, io->sum8};
+        merge_kernel<<<dim3(pl->ntiles_out, QR / MERGE_ROWS), MERGE_THREADS, 0, as_stream(stream)>>>(pl->d_merge, Opart, Mpart, Lpart, o);
+        CU(cudaGetLastError());
+    }
+    return LLATTN_OK;
+}
+
+int llattn_attention_host(llattn_ctx* c, const llattn_plan* pl, const llattn_io* h, void* stream) {
+    using namespace llattn;
+    if (!c || !pl || pl->ctx != c) return fail(LLATTN_EINVAL, "attention_host: plan does not belong to this context");
+    if (int rc = check_io(h, "attention_host")) return rc;
+    const size_t nq = size_t(pl->stats.nq_total), rows = nq * BLK;
+    const size_t bQ = rows * NQH * D * 2, bKV = rows * NKV * D * 2;
+    const size_t bO16 = h->O16 ? bQ : 0, bO32 = h->O32 ? rows * NQH * D * 4 : 0, bLSE = h->LSE ? rows * NQH * 4 : 0;
+    const size_t bq8 = h->q8 ? rows * 2048 : 0, bs8 = h->q8 ? rows * NQH * 4 : 0;
+    auto up = [](size_t x) { return (x + 255) / 256 * 256; };
+    const size_t need = up(bQ) + 2 * up(bKV) + up(bO16) + up(bO32) + up(bLSE) + up(bq8) + 2 * up(bs8);
+    {
+        std::lock_guard<std::mutex> lk(c->mu);
+        if (int rc = grow(&c->stage, &c->stage_bytes, need)) return rc;
+    }
+    uint8_t* d = static_cast<uint8_t*>(c->stage);
+    cudaStream_t st = as_stream(stream);
+    llattn_io dio{};
+    uint8_t* dQ = d; d += up(bQ);
+    uint8_t* dK = d; d += up(bKV);
+    uint8_t* dV = d; d += up(bKV);
+    dio.Q = dQ; dio.Kf = dK; dio.Vf = dV; dio.scale = h->scale;
+    if (bO16) { dio.O16 = d; d += up(bO16); }
+    if (bO32) { dio.O32 = reinterpret_cast<float*>(d); d += up(bO32); }
+    if (bLSE) { dio.LSE = reinterpret_cast<float*>(d); d += up(bLSE); }
+    if (bq8) {
+        dio.q8 = reinterpret_cast<int8_t*>(d); d += up(bq8);
+        dio.s8 = reinterpret_cast<float*>(d); d += up(bs8);
+        dio.sum8 = reinterpret_cast<int32_t*>(d); d += up(bs8);
+    }
+    CU(cudaMemcpyAsync(dQ, h->Q, bQ, cudaMemcpyHostToDevice, st));
+    CU(cudaMemcpyAsync(dK, h->Kf, bKV, cudaMemcpyHostToDevice, st));
+    CU(cudaMemcpyAsync(dV, h->Vf, bKV, cudaMemcpyHostToDevice, st));
+    if (int rc = llattn_attention(c, pl, &dio, stream)) return rc;
+    if (bO16) CU(cudaMemcpyAsync(h->O16, dio.O16, bO16, cudaMemcpyDeviceToHost, st));
+    if (bO32) CU(cudaMemcpyAsync(h->O32, dio.O32, bO32, cudaMemcpyDeviceToHost, st));
+    if (bLSE) CU(cudaMemcpyAsync(h->LSE, dio.LSE, bLSE, cudaMemcpyDeviceToHost, st));
+    if (bq8) {
+        CU(cudaMemcpyAsync(h->q8, dio.q8, bq8, cudaMemcpyDeviceToHost, st));
+        CU(cudaMemcpyAsync(h->s8, dio.s8, bs8, cudaMemcpyDeviceToHost, st));
+        CU(cudaMemcpyAsync(h->sum8, dio.sum8, bs8, cudaMemcpyDeviceToHost, st));
+    }
+    return LLATTN_OK;
+}
+
+int llattn_device_status(llattn_ctx* c, void* stream, int* code) {
+    if (!c || !code) return fail(LLATTN_EINVAL, "device_status: null pointer");
+    CU(cudaStreamSynchronize(as_stream(stream)));
+    CU(cudaMemcpy(code, c->err_word, sizeof(int), cudaMemcpyDeviceToHost));
+    if (*code) {
+        CU(cudaMemset(c->err_word, 0, sizeof(int)));
+        return fail(LLATTN_EDEVICE, "a kernel wait ran out (error bits 0x%x)", *code);
+    }
+    return LLATTN_OK;
+}
+
+}  // extern "C"

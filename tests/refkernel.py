@@ -1,0 +1,60 @@
+"""ctypes face of oracle/_ref/libattn_ref.so: the reference's own attn.cu kernels compiled for sm_100a by
+oracle/Makefile (`make ref`) where the reference checkout exists. Test infrastructure only. `available()` is False
+when the file did not travel; tests that need it skip."""
+import ctypes
+import os
+
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+PATH = os.path.join(ROOT, "oracle", "_ref", "libattn_ref.so")
+_lib = None
+
+
+def available() -> bool:
+    return os.path.exists(PATH)
+
+
+def lib():
+    global _lib
+    if _lib is None:
+        L = ctypes.CDLL(PATH)
+        vp, i = ctypes.c_void_p, ctypes.c_int
+        L.ref_pick_bpc.argtypes = [i, i]
+        L.ref_chunks_for.argtypes = [i, i]
+        L.ref_kv_commit.argtypes = [vp, vp, vp, i, i, i, vp]
+        L.ref_attention.argtypes = [vp, vp, vp, vp, i, i, i, i, vp, vp, vp, vp, vp, vp, vp, vp]
+        _lib = L
+    return _lib
+
+
+def kv_commit(Kf, Vf, cache, max_blocks, blk):
+    import torch
+    rc = lib().ref_kv_commit(Kf.data_ptr(), Vf.data_ptr(), cache.data_ptr(), max_blocks, blk, Kf.shape[0],
+                             torch.cuda.current_stream().cuda_stream)
+    assert rc == 0, rc
+
+
+def attention(Q, Kf, Vf, cache, max_blocks, nblocks, bpc=0, int8=False):
+    """Runs attn_partial + attn_combine of the reference. Returns fp16 O [nb*32][16][128] (or (q8, s8, sum8))."""
+    import torch
+    nb = Q.shape[0]
+    L = lib()
+    if bpc <= 0:
+        bpc = L.ref_pick_bpc(nblocks + nb - 1, nb)
+    nch = L.ref_chunks_for(nblocks + nb - 1, bpc)
+    dev = Q.device
+    Op = torch.empty((nb, 4, nch, 128, 128), dtype=torch.float32, device=dev)
+    Mp = torch.empty((nb, 4, nch, 128), dtype=torch.float32, device=dev)
+    Lp = torch.empty((nb, 4, nch, 128), dtype=torch.float32, device=dev)
+    O = torch.empty((nb * 32, 16, 128), dtype=torch.float16, device=dev)
+    q8 = s8 = sum8 = None
+    if int8:
+        q8 = torch.empty((nb * 32, 2048), dtype=torch.int8, device=dev)
+        s8 = torch.empty((nb * 32, 16), dtype=torch.float32, device=dev)
+        sum8 = torch.empty((nb * 32, 16), dtype=torch.int32, device=dev)
+    rc = L.ref_attention(Q.data_ptr(), Kf.data_ptr(), Vf.data_ptr(), cache.data_ptr(), max_blocks, nblocks, nb, bpc,
+                         Op.data_ptr(), Mp.data_ptr(), Lp.data_ptr(), O.data_ptr(),
+                         q8.data_ptr() if int8 else None, s8.data_ptr() if int8 else None,
+                         sum8.data_ptr() if int8 else None, torch.cuda.current_stream().cuda_stream)
+    assert rc == 0, rc
+    torch.cuda.synchronize()
+    return (q8, s8, sum8) if int8 else O
