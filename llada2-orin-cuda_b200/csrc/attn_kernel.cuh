@@ -13,7 +13,8 @@
 //                   exactly the fp16 P the numerator uses (numerator and denominator then share their rounding)
 //   softmax warps : one thread per query row (TMEM lane); row max, lazy rescale (the reference maximum moves only
 //                   when exceeded by more than 8 in log2 units, engine/attn.cu:237-255), p = 2^(s*scale*log2e - m),
-//                   P stored back over S in TMEM as fp16 pairs
+//                   P stored back over S in TMEM as fp16 pairs (keys 0-63 at columns 0-31, keys 64-127 at 64-95: each
+//                   softmax warp overwrites only S columns it has itself consumed)
 // The run's un-normalised O (fp32), reference maximum (log2 units) and row sum go to a partial slot in the format of
 // the reference's Opart/Mpart/Lpart (engine/attn.cu:291-305); merge_kernel.cuh folds the slots of a tile together.
 //
@@ -37,24 +38,31 @@ constexpr int TILE_BYTES = 16 * CS;                // 33024: Q or K tile
 constexpr int V_ROWS = 18;                         // 16 chunk rows of dims + one holding the ones column + one of zeros
 constexpr int VTILE_BYTES = V_ROWS * CS;           // 37152
 constexpr int PV_N = 144;                          // dims 0..127, column 128 = row sum, 129..143 unused
-constexpr int NRAW = 6;                            // records in flight
+constexpr int NRAW = 8;                            // records in flight (two tiles' worth)
 constexpr int RAW_STRIDE = 4864;                   // 4736 rounded up to a multiple of 128
 constexpr int SM_Q = 0;
 constexpr int SM_K = SM_Q + TILE_BYTES;            // two K tiles
 constexpr int SM_V = SM_K + 2 * TILE_BYTES;        // two V tiles
 constexpr int SM_RAW = SM_V + 2 * VTILE_BYTES;
 constexpr int SM_BAR = SM_RAW + NRAW * RAW_STRIDE;
-constexpr int SM_MISC = SM_BAR + 256;
+constexpr int SM_X = SM_BAR + 512;                 // row-max exchange between the two softmax warps of a lane quarter
+constexpr int SM_MISC = SM_X + 2 * 2 * 128 * 4;
 constexpr int ATTN_SMEM_BYTES = SM_MISC + 16;
-constexpr int ATTN_THREADS = 320;                  // warps 0-3 softmax, 4-7 dequant, 8 producer, 9 MMA
+// warps 0-7 softmax (warp w: TMEM lane quarter w % 4, key half w / 4), 8-15 dequant (two groups of four, group g takes
+// the units u of a tile with u % 2 == g), 16 producer, 17 MMA
+constexpr int SOFTMAX_WARPS = 8, DEQUANT_WARPS = 8;
+constexpr int WARP_PRODUCER = SOFTMAX_WARPS + DEQUANT_WARPS, WARP_MMA = WARP_PRODUCER + 1;
+constexpr int ATTN_THREADS = 32 * (WARP_MMA + 1);  // 576
 constexpr int TMEM_COLS = 512;
 constexpr int TM_S = 0, TM_O = 256, TM_L = TM_O + 128;   // S buffers at columns 0 and 128, O at 256..383, row sum at 384
 constexpr float RESCALE_SLACK = 8.f;
 
 // barrier indices
-enum { B_RAW_FULL = 0, B_RAW_EMPTY = B_RAW_FULL + NRAW, B_KV_FULL = B_RAW_EMPTY + NRAW, B_PV_DONE = B_KV_FULL + 2,
-       B_S_FULL = B_PV_DONE + 2, B_P_FULL = B_S_FULL + 2, B_Q_FULL = B_P_FULL + 2, B_O_FREE, B_SPARE, B_COUNT };
-static_assert(B_COUNT * 8 <= 256, "barrier area");
+enum { B_RAW_FULL = 0, B_RAW_EMPTY = B_RAW_FULL + NRAW, B_K_FULL = B_RAW_EMPTY + NRAW, B_V_FULL = B_K_FULL + 2,
+       B_K_FREE = B_V_FULL + 2, B_PV_DONE = B_K_FREE + 2, B_S_FULL = B_PV_DONE + 2, B_P_FULL = B_S_FULL + 2,
+       B_Q_FULL = B_P_FULL + 2, B_O_FREE, B_SPARE, B_XCHG, B_COUNT = B_XCHG + 4 };
+static_assert(B_COUNT * 8 <= 512, "barrier area");
+static_assert(ATTN_SMEM_BYTES <= 232448, "shared memory budget");
 
 struct KParams {
     const SeqDesc* seqs;           // list mode
@@ -127,29 +135,42 @@ __device__ __forceinline__ float ex2(float x) {
     return y;
 }
 
-// One staged record -> fp16 K and V at key offset (unit * 32) of a tile pair. dt = 0..127.
-__device__ __forceinline__ void dequant_record(const uint8_t* raw, uint8_t* Kt, uint8_t* Vt, int dt) {
+__device__ __forceinline__ float max3(float a, float b, float c) {
+    float d;
+    asm("max.f32 %0, %1, %2, %3;" : "=f"(d) : "f"(a), "f"(b), "f"(c));
+    return d;
+}
+
+// K half of one staged record -> fp16 at key offset (unit * 32) of a K tile. dt = 0..127: chunk row c = dt & 15,
+// tokens (dt >> 4) + 8 i.
+__device__ __forceinline__ void dequant_k(const uint8_t* raw, uint8_t* Kt, int dt) {
     const int c = dt & 15, tb = dt >> 4;
     const uint4 s4 = permute8(*reinterpret_cast<const uint4*>(raw + KOFF_META + c * 16));
     const uint4 m4 = permute8(*reinterpret_cast<const uint4*>(raw + KOFF_META + 256 + c * 16));
     const half2* ks = reinterpret_cast<const half2*>(&s4);
     const half2* km = reinterpret_cast<const half2*>(&m4);
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+        const int tok = tb + 8 * i;
+        half2 kh[4];
+        unpack8(*reinterpret_cast<const uint32_t*>(raw + tok * 64 + c * 4), kh);
+#pragma unroll
+        for (int j = 0; j < 4; ++j) kh[j] = __hfma2(kh[j], ks[j], km[j]);
+        *reinterpret_cast<uint4*>(Kt + c * CS + tok * 16) = *reinterpret_cast<const uint4*>(kh);
+    }
+}
+// V half: scale and min per token.
+__device__ __forceinline__ void dequant_v(const uint8_t* raw, uint8_t* Vt, int dt) {
+    const int c = dt & 15, tb = dt >> 4;
     const half* vmeta = reinterpret_cast<const half*>(raw + VOFF_META);
 #pragma unroll
     for (int i = 0; i < 4; ++i) {
         const int tok = tb + 8 * i;
-        const uint32_t kw = *reinterpret_cast<const uint32_t*>(raw + tok * 64 + c * 4);
-        const uint32_t vw = *reinterpret_cast<const uint32_t*>(raw + VOFF + tok * 64 + c * 4);
         const half2 vs = __half2half2(vmeta[tok]), vm = __half2half2(vmeta[BLK + tok]);
-        half2 kh[4], vh[4];
-        unpack8(kw, kh);
-        unpack8(vw, vh);
+        half2 vh[4];
+        unpack8(*reinterpret_cast<const uint32_t*>(raw + VOFF + tok * 64 + c * 4), vh);
 #pragma unroll
-        for (int j = 0; j < 4; ++j) {
-            kh[j] = __hfma2(kh[j], ks[j], km[j]);
-            vh[j] = __hfma2(vh[j], vs, vm);
-        }
-        *reinterpret_cast<uint4*>(Kt + c * CS + tok * 16) = *reinterpret_cast<const uint4*>(kh);
+        for (int j = 0; j < 4; ++j) vh[j] = __hfma2(vh[j], vs, vm);
         *reinterpret_cast<uint4*>(Vt + c * CS + tok * 16) = *reinterpret_cast<const uint4*>(vh);
     }
 }
@@ -170,23 +191,29 @@ __global__ void __launch_bounds__(ATTN_THREADS, 1) attn_tile_kernel(const __grid
     if (tid == 0) {
         for (int i = 0; i < NRAW; ++i) { ptx::mbar_init(BAR(B_RAW_FULL + i), 1); ptx::mbar_init(BAR(B_RAW_EMPTY + i), 128); }
         for (int i = 0; i < 2; ++i) {
-            ptx::mbar_init(BAR(B_KV_FULL + i), 128); ptx::mbar_init(BAR(B_PV_DONE + i), 1);
-            ptx::mbar_init(BAR(B_S_FULL + i), 1); ptx::mbar_init(BAR(B_P_FULL + i), 128);
+            ptx::mbar_init(BAR(B_K_FULL + i), 32 * DEQUANT_WARPS); ptx::mbar_init(BAR(B_V_FULL + i), 32 * DEQUANT_WARPS);
+            ptx::mbar_init(BAR(B_K_FREE + i), 1); ptx::mbar_init(BAR(B_PV_DONE + i), 1);
+            ptx::mbar_init(BAR(B_S_FULL + i), 1); ptx::mbar_init(BAR(B_P_FULL + i), 32 * SOFTMAX_WARPS);
         }
-        ptx::mbar_init(BAR(B_Q_FULL), 128); ptx::mbar_init(BAR(B_O_FREE), 128); ptx::mbar_init(BAR(B_SPARE), 1);
+        ptx::mbar_init(BAR(B_Q_FULL), 32 * DEQUANT_WARPS); ptx::mbar_init(BAR(B_O_FREE), 32 * SOFTMAX_WARPS);
+        ptx::mbar_init(BAR(B_SPARE), 1);
+        for (int i = 0; i < 4; ++i) ptx::mbar_init(BAR(B_XCHG + i), 64);
         ptx::fence_mbar_init();
         *abort_flag = 0;
     }
-    if (warp == 9) { ptx::tmem_alloc(ptx::smem_u32(tmem_slot), TMEM_COLS); ptx::tmem_relinquish(); }
+    if (warp == WARP_MMA) { ptx::tmem_alloc(ptx::smem_u32(tmem_slot), TMEM_COLS); ptx::tmem_relinquish(); }
     ptx::tc_fence_before();
     __syncthreads();
     ptx::tc_fence_after();
     const uint32_t tmem = *tmem_slot;
     int errbits = 0;
 
-    if (warp < 4) {
-        // ================================================================== softmax + epilogue: thread = query row
-        const uint32_t tlane = tmem + (uint32_t(warp * 32) << 16);
+    if (warp < SOFTMAX_WARPS) {
+        // ================================================================== softmax + epilogue
+        // thread = (query row, key half): the warp pair (w, w ^ 4) shares TMEM lanes and splits a tile's keys 0-63 / 64-127
+        const int q = warp & 3, hf = warp >> 2, row = q * 32 + lane;
+        const uint32_t tlane = tmem + (uint32_t(q * 32) << 16);
+        float* xb = reinterpret_cast<float*>(smem + SM_X);
         uint32_t t = 0;
         bool alive = true;
 #pragma unroll 1
@@ -198,36 +225,43 @@ __global__ void __launch_bounds__(ATTN_THREADS, 1) attn_tile_kernel(const __grid
 #pragma unroll 1
             for (int i = 0; i < ntiles; ++i, ++t) {
                 const int b = t & 1, nu = min(TILE_UNITS, U - TILE_UNITS * i);
+                const int nc = max(0, min(2, nu - 2 * hf));          // 32-key chunks of this tile this warp owns
                 if (!ptx::mbar_wait(BAR(B_S_FULL + b), (t >> 1) & 1, abort_flag)) { alive = false; errbits |= ERR_WAIT_SOFTMAX; break; }
                 ptx::tc_fence_after();
                 const uint32_t ts = tlane + TM_S + b * 128;
                 float mx = -INFINITY;
 #pragma unroll 1
-                for (int c = 0; c < nu; ++c) {
+                for (int c = 0; c < nc; ++c) {
                     uint32_t r[32];
-                    ptx::tmem_ld32(ts + 32 * c, r);
+                    ptx::tmem_ld32(ts + 64 * hf + 32 * c, r);
                     ptx::tmem_wait_ld();
 #pragma unroll
-                    for (int j = 0; j < 32; ++j) mx = fmaxf(mx, __uint_as_float(r[j]));
+                    for (int j = 0; j < 32; j += 2) mx = max3(mx, __uint_as_float(r[j]), __uint_as_float(r[j + 1]));
                 }
+                // row max over both halves: exchange through shared memory with the partner warp (double-buffered by
+                // tile parity; the pair's mbarrier, one phase per tile, orders write -> read and its wait is bounded)
+                xb[b * 256 + hf * 128 + row] = mx;
+                ptx::mbar_arrive(BAR(B_XCHG + q));
+                if (!ptx::mbar_wait(BAR(B_XCHG + q), t & 1, abort_flag)) { alive = false; errbits |= ERR_WAIT_SOFTMAX; break; }
+                mx = fmaxf(mx, xb[b * 256 + (hf ^ 1) * 128 + row]);
                 const float msc = mx * p.sl2;
                 const bool moved = msc > mref + RESCALE_SLACK;
                 if (i > 0 && __any_sync(0xffffffffu, moved)) {
-                    // the accumulated O of this row group is rescaled to the new reference maximum; every PV issued
-                    // so far must have landed first
+                    // the accumulated O of these rows is rescaled to the new reference maximum (this warp's half of the
+                    // columns); every PV issued so far must have landed first
                     if (!ptx::mbar_wait(BAR(B_PV_DONE + (b ^ 1)), ((t - 1) >> 1) & 1, abort_flag)) { alive = false; errbits |= ERR_WAIT_SOFTMAX; break; }
                     ptx::tc_fence_after();
                     const float corr = moved ? ex2(mref - msc) : 1.f;
 #pragma unroll 1
-                    for (int c = 0; c < 4; ++c) {
+                    for (int c = 0; c < 2; ++c) {
                         uint32_t r[32];
-                        ptx::tmem_ld32(tlane + TM_O + 32 * c, r);
+                        ptx::tmem_ld32(tlane + TM_O + 64 * hf + 32 * c, r);
                         ptx::tmem_wait_ld();
 #pragma unroll
                         for (int j = 0; j < 32; ++j) r[j] = __float_as_uint(__uint_as_float(r[j]) * corr);
-                        ptx::tmem_st32(tlane + TM_O + 32 * c, r);
+                        ptx::tmem_st32(tlane + TM_O + 64 * hf + 32 * c, r);
                     }
-                    {
+                    if (hf == 1) {
                         uint32_t r[16];
                         ptx::tmem_ld16(tlane + TM_L, r);
                         ptx::tmem_wait_ld();
@@ -238,9 +272,9 @@ __global__ void __launch_bounds__(ATTN_THREADS, 1) attn_tile_kernel(const __grid
                 }
                 if (moved) mref = msc;
 #pragma unroll 1
-                for (int c = 0; c < nu; ++c) {
+                for (int c = 0; c < nc; ++c) {
                     uint32_t r[32], pk[16];
-                    ptx::tmem_ld32(ts + 32 * c, r);
+                    ptx::tmem_ld32(ts + 64 * hf + 32 * c, r);
                     ptx::tmem_wait_ld();
 #pragma unroll
                     for (int j = 0; j < 16; ++j) {
@@ -249,22 +283,22 @@ __global__ void __launch_bounds__(ATTN_THREADS, 1) attn_tile_kernel(const __grid
                         const half2 h = __floats2half2_rn(p0, p1);
                         pk[j] = *reinterpret_cast<const uint32_t*>(&h);
                     }
-                    ptx::tmem_st16(ts + 16 * c, pk);
+                    ptx::tmem_st16(ts + 64 * hf + 16 * c, pk);      // P chunk over S columns this warp has already consumed
                 }
                 ptx::tmem_wait_st();
                 ptx::tc_fence_before();
                 ptx::mbar_arrive(BAR(B_P_FULL + b));
             }
             if (!alive) break;
-            // ---- epilogue: un-normalised O, reference maximum and row sum of this run
+            // ---- epilogue: un-normalised O (this warp's half of the columns), reference maximum and row sum of the run
             const uint32_t tl = t - 1;
             if (!ptx::mbar_wait(BAR(B_PV_DONE + (tl & 1)), (tl >> 1) & 1, abort_flag)) { alive = false; errbits |= ERR_WAIT_SOFTMAX; break; }
             ptx::tc_fence_after();
-            float* orow = p.Opart + (size_t(w.slot) * QR + tid) * D;
+            float* orow = p.Opart + (size_t(w.slot) * QR + row) * D + 64 * hf;
 #pragma unroll 1
-            for (int c = 0; c < 4; ++c) {
+            for (int c = 0; c < 2; ++c) {
                 uint32_t r[32];
-                ptx::tmem_ld32(tlane + TM_O + 32 * c, r);
+                ptx::tmem_ld32(tlane + TM_O + 64 * hf + 32 * c, r);
                 ptx::tmem_wait_ld();
 #pragma unroll
                 for (int g = 0; g < 4; ++g) {      // positions (0..7) hold dims (0,4,1,5,2,6,3,7)
@@ -276,28 +310,30 @@ __global__ void __launch_bounds__(ATTN_THREADS, 1) attn_tile_kernel(const __grid
                     *reinterpret_cast<float4*>(orow + 32 * c + 8 * g + 4) = hi;
                 }
             }
-            {
+            if (hf == 1) {
                 uint32_t r[16];
                 ptx::tmem_ld16(tlane + TM_L, r);
                 ptx::tmem_wait_ld();
-                p.Lpart[size_t(w.slot) * QR + tid] = __uint_as_float(r[0]);
+                p.Lpart[size_t(w.slot) * QR + row] = __uint_as_float(r[0]);
+            } else {
+                p.Mpart[size_t(w.slot) * QR + row] = mref;
             }
-            p.Mpart[size_t(w.slot) * QR + tid] = mref;
             ptx::tc_fence_before();
             ptx::mbar_arrive(BAR(B_O_FREE));
         }
-    } else if (warp < 8) {
+    } else if (warp < WARP_PRODUCER) {
         // ================================================================== dequant: records -> fp16 operand tiles
-        const int dt = tid - 128;
+        const int da = tid - 32 * SOFTMAX_WARPS;      // 0..255 over both groups
+        const int grp = da >> 7, dt = da & 127;       // group g owns the units u of a tile with u % 2 == g
         uint32_t t = 0, r = 0;
         int prev_last = -1;
         bool alive = true;
         // chunk row 16 of both V tiles: (1, 0, 0, 0, 0, 0, 0, 0) for every key -> O column 128 accumulates sum(P);
-        // chunk row 17: zeros. Published by the first kv_full arrival.
-        for (int idx = dt; idx < 2 * 2 * 128; idx += 128) {
-            const int buf = idx >> 8, row = (idx >> 7) & 1, key = idx & 127;
-            *reinterpret_cast<uint4*>(smem + SM_V + buf * VTILE_BYTES + (16 + row) * CS + key * 16) =
-                make_uint4(row == 0 ? 0x00003C00u : 0u, 0u, 0u, 0u);
+        // chunk row 17: zeros. Published by the first v_full arrival.
+        for (int idx = da; idx < 2 * 2 * 128; idx += 256) {
+            const int buf = idx >> 8, rw = (idx >> 7) & 1, key = idx & 127;
+            *reinterpret_cast<uint4*>(smem + SM_V + buf * VTILE_BYTES + (16 + rw) * CS + key * 16) =
+                make_uint4(rw == 0 ? 0x00003C00u : 0u, 0u, 0u, 0u);
         }
 #pragma unroll 1
         for (int ii = i0; ii < i1 && alive; ++ii) {
@@ -305,49 +341,68 @@ __global__ void __launch_bounds__(ATTN_THREADS, 1) attn_tile_kernel(const __grid
             if (!fetch_item(p, ii, w, s)) continue;
             const int U = w.rec_count + w.fresh, ntiles = (U + TILE_UNITS - 1) / TILE_UNITS;
             const size_t qg = size_t(s.q_first + w.qblk);
-            if (prev_last >= 0 &&      // Q is overwritten: every MMA of the previous item must be done
-                !ptx::mbar_wait(BAR(B_PV_DONE + (prev_last & 1)), (uint32_t(prev_last) >> 1) & 1, abort_flag)) { alive = false; errbits |= ERR_WAIT_DEQUANT; break; }
+            const size_t f0 = (qg * BLK) * NKV * D + size_t(w.kvh) * D;
+            if (prev_last >= 0 &&      // Q is overwritten: every S MMA of the previous item must be done
+                !ptx::mbar_wait(BAR(B_K_FREE + (prev_last & 1)), (uint32_t(prev_last) >> 1) & 1, abort_flag)) { alive = false; errbits |= ERR_WAIT_DEQUANT; break; }
 #pragma unroll 4
-            for (int i = 0; i < 16; ++i) {
-                const int idx = dt + 128 * i, row = idx >> 4, ch = idx & 15;
-                const half* src = p.Q + ((qg * BLK + (row >> 2)) * NQH + 4 * w.kvh + (row & 3)) * D + ch * 8;
-                *reinterpret_cast<uint4*>(smem + SM_Q + ch * CS + row * 16) = permute8(__ldg(reinterpret_cast<const uint4*>(src)));
+            for (int i = 0; i < 8; ++i) {
+                const int idx = da + 256 * i, rw = idx >> 4, ch = idx & 15;
+                const half* src = p.Q + ((qg * BLK + (rw >> 2)) * NQH + 4 * w.kvh + (rw & 3)) * D + ch * 8;
+                *reinterpret_cast<uint4*>(smem + SM_Q + ch * CS + rw * 16) = permute8(__ldg(reinterpret_cast<const uint4*>(src)));
             }
             ptx::fence_proxy_async_smem();
             ptx::mbar_arrive(BAR(B_Q_FULL));
 #pragma unroll 1
             for (int i = 0; i < ntiles && alive; ++i, ++t) {
                 const int b = t & 1, nu = min(TILE_UNITS, U - TILE_UNITS * i);
-                if (t >= 2 && !ptx::mbar_wait(BAR(B_PV_DONE + b), ((t >> 1) - 1) & 1, abort_flag)) { alive = false; errbits |= ERR_WAIT_DEQUANT; break; }
                 uint8_t* Kt = smem + SM_K + b * TILE_BYTES;
                 uint8_t* Vt = smem + SM_V + b * VTILE_BYTES;
+                // ---- K: the tile's K buffer is free once S of tile t-2 has been computed
+                if (t >= 2 && !ptx::mbar_wait(BAR(B_K_FREE + b), ((t >> 1) - 1) & 1, abort_flag)) { alive = false; errbits |= ERR_WAIT_DEQUANT; break; }
 #pragma unroll 1
-                for (int u = 0; u < nu; ++u) {
+                for (int u = grp; u < nu; u += 2) {
                     const int unit = TILE_UNITS * i + u;
                     if (unit < w.rec_count) {
-                        const uint32_t slot = r % NRAW;
-                        if (!ptx::mbar_wait(BAR(B_RAW_FULL + slot), (r / NRAW) & 1, abort_flag)) { alive = false; errbits |= ERR_WAIT_DEQUANT; break; }
-                        dequant_record(smem + SM_RAW + slot * RAW_STRIDE, Kt + u * 512, Vt + u * 512, dt);
-                        ptx::mbar_arrive(BAR(B_RAW_EMPTY + slot));
-                        ++r;
-                    } else {          // the query block's own K/V, exact fp16
-                        const size_t f0 = (qg * BLK) * NKV * D + size_t(w.kvh) * D;
+                        const uint32_t rr = r + u, slot = rr % NRAW;
+                        if (!ptx::mbar_wait(BAR(B_RAW_FULL + slot), (rr / NRAW) & 1, abort_flag)) { alive = false; errbits |= ERR_WAIT_DEQUANT; break; }
+                        dequant_k(smem + SM_RAW + slot * RAW_STRIDE, Kt + u * 512, dt);
+                    } else {          // the query block's own K, exact fp16
 #pragma unroll
                         for (int k = 0; k < 4; ++k) {
                             const int idx = dt + 128 * k, tok = idx >> 4, ch = idx & 15;
-                            const size_t off = f0 + size_t(tok) * NKV * D + ch * 8;
-                            *reinterpret_cast<uint4*>(Kt + u * 512 + ch * CS + tok * 16) = permute8(__ldg(reinterpret_cast<const uint4*>(p.Kf + off)));
-                            *reinterpret_cast<uint4*>(Vt + u * 512 + ch * CS + tok * 16) = permute8(__ldg(reinterpret_cast<const uint4*>(p.Vf + off)));
+                            *reinterpret_cast<uint4*>(Kt + u * 512 + ch * CS + tok * 16) =
+                                permute8(__ldg(reinterpret_cast<const uint4*>(p.Kf + f0 + size_t(tok) * NKV * D + ch * 8)));
                         }
                     }
                 }
                 if (!alive) break;
                 ptx::fence_proxy_async_smem();
-                ptx::mbar_arrive(BAR(B_KV_FULL + b));
+                ptx::mbar_arrive(BAR(B_K_FULL + b));
+                // ---- V: free once PV of tile t-2 has been computed
+                if (t >= 2 && !ptx::mbar_wait(BAR(B_PV_DONE + b), ((t >> 1) - 1) & 1, abort_flag)) { alive = false; errbits |= ERR_WAIT_DEQUANT; break; }
+#pragma unroll 1
+                for (int u = grp; u < nu; u += 2) {
+                    const int unit = TILE_UNITS * i + u;
+                    if (unit < w.rec_count) {
+                        const uint32_t slot = (r + u) % NRAW;       // landed: the K pass waited for it
+                        dequant_v(smem + SM_RAW + slot * RAW_STRIDE, Vt + u * 512, dt);
+                        ptx::mbar_arrive(BAR(B_RAW_EMPTY + slot));
+                    } else {
+#pragma unroll
+                        for (int k = 0; k < 4; ++k) {
+                            const int idx = dt + 128 * k, tok = idx >> 4, ch = idx & 15;
+                            *reinterpret_cast<uint4*>(Vt + u * 512 + ch * CS + tok * 16) =
+                                permute8(__ldg(reinterpret_cast<const uint4*>(p.Vf + f0 + size_t(tok) * NKV * D + ch * 8)));
+                        }
+                    }
+                }
+                ptx::fence_proxy_async_smem();
+                ptx::mbar_arrive(BAR(B_V_FULL + b));
+                r += uint32_t(min(nu, max(0, w.rec_count - TILE_UNITS * i)));     // records of this tile (both groups count alike)
             }
             prev_last = int(t) - 1;
         }
-    } else if (warp == 8) {
+    } else if (warp == WARP_PRODUCER) {
         // ================================================================== producer: bulk copies of records
         uint32_t r = 0;
         bool alive = true;
@@ -386,12 +441,13 @@ __global__ void __launch_bounds__(ATTN_THREADS, 1) attn_tile_kernel(const __grid
         const uint32_t idO = ptx::idesc_f16(128, PV_N, false, true);
         auto issue_pv = [&](uint32_t tt, int nu, bool first) -> bool {
             const uint32_t bb = tt & 1;
+            if (!ptx::mbar_wait(BAR(B_V_FULL + bb), (tt >> 1) & 1, abort_flag)) return false;
             if (!ptx::mbar_wait(BAR(B_P_FULL + bb), (tt >> 1) & 1, abort_flag)) return false;
             if (first && itc > 0 && !ptx::mbar_wait(BAR(B_O_FREE), (itc - 1) & 1, abort_flag)) return false;
             ptx::tc_fence_after();
             if (lane == 0) {
                 for (int j = 0; j < 2 * nu; ++j)   // 16 keys per step: B is MN-major, 8-key groups 128 B apart, dim groups CS apart
-                    ptx::mma_ts(tmem + TM_O, tmem + TM_S + bb * 128 + j * 8,
+                    ptx::mma_ts(tmem + TM_O, tmem + TM_S + bb * 128 + (j >> 2) * 64 + (j & 3) * 8,
                                 ptx::smem_desc(v_s + bb * VTILE_BYTES + j * 256, 128, CS), idO, (first && j == 0) ? 0u : 1u);
                 ptx::mma_commit(BAR(B_PV_DONE + bb));
             }
@@ -409,7 +465,7 @@ __global__ void __launch_bounds__(ATTN_THREADS, 1) attn_tile_kernel(const __grid
             for (int i = 0; i < ntiles; ++i, ++t) {
                 const uint32_t b = t & 1;
                 const int nu = min(TILE_UNITS, U - TILE_UNITS * i);
-                if (!ptx::mbar_wait(BAR(B_KV_FULL + b), (t >> 1) & 1, abort_flag)) { alive = false; errbits |= ERR_WAIT_MMA; break; }
+                if (!ptx::mbar_wait(BAR(B_K_FULL + b), (t >> 1) & 1, abort_flag)) { alive = false; errbits |= ERR_WAIT_MMA; break; }
                 ptx::tc_fence_after();
                 if (lane == 0) {
                     const uint32_t idS = ptx::idesc_f16(128, 32 * nu, false, false);
@@ -418,6 +474,7 @@ __global__ void __launch_bounds__(ATTN_THREADS, 1) attn_tile_kernel(const __grid
                         ptx::mma_ss(tmem + TM_S + b * 128, ptx::smem_desc(q_s + 2 * j * CS, CS, 128),
                                     ptx::smem_desc(k_s + b * TILE_BYTES + 2 * j * CS, CS, 128), idS, j > 0 ? 1u : 0u);
                     ptx::mma_commit(BAR(B_S_FULL + b));
+                    ptx::mma_commit(BAR(B_K_FREE + b));
                 }
                 __syncwarp();
                 if (i > 0 && !issue_pv(t - 1, nu_prev, i == 1)) { alive = false; errbits |= ERR_WAIT_MMA; break; }
@@ -439,7 +496,7 @@ __global__ void __launch_bounds__(ATTN_THREADS, 1) attn_tile_kernel(const __grid
     if (errbits && p.err) atomicOr(p.err, errbits);
     ptx::tc_fence_before();
     __syncthreads();
-    if (warp == 9) ptx::tmem_dealloc(tmem, TMEM_COLS);
+    if (warp == WARP_MMA) ptx::tmem_dealloc(tmem, TMEM_COLS);
 }
 
 }  // namespace llattn
