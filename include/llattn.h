@@ -133,6 +133,12 @@ int llattn_plan_create(llattn_ctx* ctx, const llattn_seq* seqs_host, int nseq, i
 void llattn_plan_destroy(llattn_plan* plan);
 int llattn_plan_get_stats(const llattn_plan* plan, llattn_plan_stats* out);
 
+/* The planner alone, on the host (no CUDA call): statistics of the plan llattn_plan_create would build and, when the
+ * arrays are given, its work items (8 int32 each: sequence, query block, kv head, first record, record count, fresh
+ * flag, partial slot, 0) and the per-CTA item ranges (nctas + 1 bounds). For sizing and for host-side tests. */
+int llattn_plan_preview(const llattn_seq* seqs_host, int nseq, int nctas, llattn_plan_stats* stats, int32_t* items_out,
+                        int max_items, int32_t* cta_first_out, int max_ctas);
+
 /* One attention pass over every sequence of the plan: kernel launches only (two), no allocation, no host sync. */
 int llattn_attention(llattn_ctx* ctx, const llattn_plan* plan, const llattn_io* io, void* stream);
 

@@ -4,4 +4,4 @@ The package holds the CUDA sources (csrc/), the build step for the C-ABI shared 
 mirrors the reference's `attn` operator interface, the seeded workload generator and the request-sharding
 helper. There is no CPU or PyTorch fallback: every compute entry point needs the built CUDA library and a GPU.
 """
-from . import workload  # noqa: F401
+from . import sharding, workload  # noqa: F401

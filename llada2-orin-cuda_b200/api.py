@@ -25,7 +25,7 @@ OK, EINVAL, ECUDA, ENOMEM, EDEVICE = 0, 1, 2, 3, 4
 EXPORTS = (
     "llattn_version", "llattn_last_error", "llattn_pick_bpc", "llattn_chunks_for", "llattn_kv_commit",
     "llattn_kv_commit_paged", "llattn_attn_partial", "llattn_attn_combine", "llattn_create", "llattn_destroy",
-    "llattn_plan_create", "llattn_plan_destroy", "llattn_plan_get_stats", "llattn_attention",
+    "llattn_plan_create", "llattn_plan_destroy", "llattn_plan_get_stats", "llattn_plan_preview", "llattn_attention",
     "llattn_attention_parts", "llattn_attention_host", "llattn_device_status",
 )
 
@@ -83,6 +83,7 @@ def lib() -> ctypes.CDLL:
         L.llattn_plan_destroy.argtypes = [c_void_p]
         L.llattn_plan_destroy.restype = None
         L.llattn_plan_get_stats.argtypes = [c_void_p, POINTER(PlanStats)]
+        L.llattn_plan_preview.argtypes = [POINTER(_Seq), c_int, c_int, POINTER(PlanStats), c_void_p, c_int, c_void_p, c_int]
         L.llattn_attention.argtypes = [c_void_p, c_void_p, POINTER(_IO), c_void_p]
         L.llattn_attention_parts.argtypes = [c_void_p, c_void_p, POINTER(_IO), c_int, c_void_p]
         L.llattn_attention_host.argtypes = [c_void_p, c_void_p, POINTER(_IO), c_void_p]
@@ -192,6 +193,24 @@ class Seq:
         if hs is None:
             hs = self.pages.shape[-1] if self.pages is not None else (self.cache.shape[1] if self.cache is not None else 0)
         return _Seq(_ptr(self.cache), _ptr(self.pages), hs, self.nblocks, self.nq, self.q_first)
+
+
+def plan_preview(lengths, nctas: int, nq=None):
+    """Host-only planner run (no GPU needed): lengths[i] = committed blocks of sequence i, nq[i] its query blocks.
+    Returns (PlanStats, items int32 [n][8], cta_first int32 [nctas_used + 1])."""
+    import numpy as np
+    n = len(lengths)
+    nq = [1] * n if nq is None else list(nq)
+    q0, arr = 0, (_Seq * n)()
+    for i in range(n):
+        arr[i] = _Seq(0x1000, None, int(lengths[i]) + nq[i], int(lengths[i]), nq[i], q0)   # placeholder, aligned cache address
+        q0 += nq[i]
+    st = PlanStats()
+    _check(lib().llattn_plan_preview(arr, n, nctas, byref(st), None, 0, None, 0))
+    items = np.zeros((st.nitems, 8), np.int32)
+    cta_first = np.zeros(st.nctas + 1, np.int32)
+    _check(lib().llattn_plan_preview(arr, n, nctas, byref(st), items.ctypes.data, st.nitems, cta_first.ctypes.data, st.nctas))
+    return st, items, cta_first
 
 
 class Context:

@@ -175,7 +175,9 @@ __device__ __forceinline__ void dequant_v(const uint8_t* raw, uint8_t* Vt, int d
     }
 }
 
-__global__ void __launch_bounds__(ATTN_THREADS, 1) attn_tile_kernel(const __grid_constant__ KParams p) {
+// The whole CTA's work. `cta` is the CTA's index in the plan (list mode) or in the flattened reference grid
+// (kv head fastest, then chunk, then query block).
+__device__ __forceinline__ void attn_tile_body(const KParams& p, const int cta) {
     extern __shared__ __align__(128) uint8_t smem[];
     uint64_t* bars = reinterpret_cast<uint64_t*>(smem + SM_BAR);
     uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(smem + SM_MISC);
@@ -185,8 +187,8 @@ __global__ void __launch_bounds__(ATTN_THREADS, 1) attn_tile_kernel(const __grid
     auto BAR = [&](int i) -> uint32_t { return bar0 + 8u * uint32_t(i); };
 
     int i0, i1;
-    if (p.items) { i0 = p.cta_first[blockIdx.x]; i1 = p.cta_first[blockIdx.x + 1]; }
-    else { i0 = blockIdx.x; i1 = blockIdx.x + 1; }
+    if (p.items) { i0 = p.cta_first[cta]; i1 = p.cta_first[cta + 1]; }
+    else { i0 = cta; i1 = cta + 1; }
 
     if (tid == 0) {
         for (int i = 0; i < NRAW; ++i) { ptx::mbar_init(BAR(B_RAW_FULL + i), 1); ptx::mbar_init(BAR(B_RAW_EMPTY + i), 128); }
@@ -497,6 +499,10 @@ __global__ void __launch_bounds__(ATTN_THREADS, 1) attn_tile_kernel(const __grid
     ptx::tc_fence_before();
     __syncthreads();
     if (warp == WARP_MMA) ptx::tmem_dealloc(tmem, TMEM_COLS);
+}
+
+__global__ void __launch_bounds__(ATTN_THREADS, 1) attn_tile_kernel(const __grid_constant__ KParams p) {
+    attn_tile_body(p, blockIdx.x);
 }
 
 }  // namespace llattn

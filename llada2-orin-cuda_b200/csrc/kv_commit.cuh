@@ -24,9 +24,9 @@ __device__ __forceinline__ uint32_t commit_code(float v, float m0, float s) {
 // Kf, Vf: [nb][32 tok][4 heads][128] fp16. Record of (input block j, head h):
 //   pages == nullptr: records + (h * max_blocks + blk + j) * 4736      (the reference's contiguous layer cache)
 //   pages != nullptr: records + pages[j * 4 + h] * 4736                (record pool)
-__global__ void __launch_bounds__(COMMIT_THREADS)
-kv_commit_kernel(const half* __restrict__ Kf, const half* __restrict__ Vf, uint8_t* __restrict__ records,
-                 const int32_t* __restrict__ pages, int max_blocks, int blk) {
+__device__ __forceinline__ void kv_commit_body(const half* __restrict__ Kf, const half* __restrict__ Vf,
+                                               uint8_t* __restrict__ records, const int32_t* __restrict__ pages,
+                                               int max_blocks, int blk) {
     __shared__ __align__(16) half Ks[BLK][D + 8];            // +8 halves: rows 272 B apart, 16-byte aligned
     __shared__ __align__(16) uint8_t kq[BLK][D];             // one code per byte before packing
     __shared__ __align__(16) uint8_t rec[REC_BYTES];
@@ -101,6 +101,12 @@ kv_commit_kernel(const half* __restrict__ Kf, const half* __restrict__ Vf, uint8
     __syncthreads();
     for (int i = tid; i < REC_BYTES / 16; i += COMMIT_THREADS)
         reinterpret_cast<uint4*>(dst)[i] = reinterpret_cast<const uint4*>(rec)[i];
+}
+
+__global__ void __launch_bounds__(COMMIT_THREADS)
+kv_commit_kernel(const half* __restrict__ Kf, const half* __restrict__ Vf, uint8_t* __restrict__ records,
+                 const int32_t* __restrict__ pages, int max_blocks, int blk) {
+    kv_commit_body(Kf, Vf, records, pages, max_blocks, blk);
 }
 
 }  // namespace llattn

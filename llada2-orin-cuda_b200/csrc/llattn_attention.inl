@@ -40,13 +40,23 @@ int build_plan(const llattn_seq* seqs, int nseq, int nctas, HostPlan& hp) {
     hp.total_units = total;
     hp.nq_total = nq_total;
     constexpr int64_t MIN_UNITS = 16;
-    int64_t share = (total + nctas - 1) / nctas;
-    share = std::max<int64_t>(share, MIN_UNITS);
-    share = (share + TILE_UNITS - 1) / TILE_UNITS * TILE_UNITS;
+    // The share of the CTA being filled is re-derived from what is left (units and CTAs), so rounding a cut down to a
+    // tile boundary never pushes work into an extra CTA: the plan uses at most `nctas` CTAs.
+    int64_t left = total;
+    int ctas_left = nctas;
+    auto new_share = [&]() -> int64_t {
+        int64_t sh = ctas_left > 1 ? (left + ctas_left - 1) / ctas_left : left;
+        sh = std::max<int64_t>(sh, MIN_UNITS);
+        return (sh + TILE_UNITS - 1) / TILE_UNITS * TILE_UNITS;
+    };
     hp.cta_first.assign(1, 0);
-    int64_t room = share;      // units the current CTA can still take
+    int64_t room = new_share();      // units the current CTA can still take
     int slot = 0;
-    auto next_cta = [&]() { hp.cta_first.push_back(int32_t(hp.items.size())); room = share; };
+    auto next_cta = [&]() {
+        hp.cta_first.push_back(int32_t(hp.items.size()));
+        if (ctas_left > 1) --ctas_left;
+        room = new_share();
+    };
     for (int s = 0; s < nseq; ++s)
         for (int j = 0; j < seqs[s].nq; ++j)
             for (int h = 0; h < NKV; ++h) {
@@ -62,7 +72,8 @@ int build_plan(const llattn_seq* seqs, int nseq, int nctas, HostPlan& hp) {
                     hp.items.push_back(WorkItem{s, j, h, done, std::max(rec_cnt, 0), done + take == U ? 1 : 0, slot++, 0});
                     done += take;
                     room -= take;
-                    if (room <= 0) next_cta();
+                    left -= take;
+                    if (room <= 0 && left > 0) next_cta();
                 }
                 hp.merge.push_back(MergeDesc{seqs[s].q_first + j, h, slot0, slot - slot0});
             }
@@ -208,6 +219,32 @@ int llattn_plan_create(llattn_ctx* c, const llattn_seq* seqs, int nseq, int ncta
     pl->stats.workspace_bytes = hp.items.size() * (SLOT_O_BYTES + 2 * SLOT_ML_BYTES);
     if (int rc = grow(&c->workspace, &c->workspace_bytes, pl->stats.workspace_bytes)) { cudaFree(pl->dev_blob); delete pl; return rc; }
     *out = pl;
+    return LLATTN_OK;
+}
+
+int llattn_plan_preview(const llattn_seq* seqs, int nseq, int nctas, llattn_plan_stats* stats, int32_t* items_out,
+                        int max_items, int32_t* cta_first_out, int max_ctas) {
+    using namespace llattn;
+    if (!seqs || !stats) return fail(LLATTN_EINVAL, "plan_preview: null pointer");
+    if (nseq < 1 || nctas < 1) return fail(LLATTN_EINVAL, "plan_preview: nseq and nctas must be positive");
+    HostPlan hp;
+    if (int rc = build_plan(seqs, nseq, nctas, hp)) return rc;
+    memset(stats, 0, sizeof(*stats));
+    stats->nseq = nseq;
+    stats->nq_total = hp.nq_total;
+    stats->nitems = stats->nslots = int32_t(hp.items.size());
+    stats->nctas = int32_t(hp.cta_first.size()) - 1;
+    stats->total_units = hp.total_units;
+    stats->max_cta_units = hp.max_cta_units;
+    stats->workspace_bytes = hp.items.size() * (SLOT_O_BYTES + 2 * SLOT_ML_BYTES);
+    if (items_out) {
+        if (max_items < int(hp.items.size())) return fail(LLATTN_ENOMEM, "plan_preview: %zu items, room for %d", hp.items.size(), max_items);
+        memcpy(items_out, hp.items.data(), hp.items.size() * sizeof(WorkItem));
+    }
+    if (cta_first_out) {
+        if (max_ctas + 1 < int(hp.cta_first.size())) return fail(LLATTN_ENOMEM, "plan_preview: %zu CTA bounds, room for %d", hp.cta_first.size(), max_ctas + 1);
+        memcpy(cta_first_out, hp.cta_first.data(), hp.cta_first.size() * sizeof(int32_t));
+    }
     return LLATTN_OK;
 }
 
