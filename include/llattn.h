@@ -150,6 +150,26 @@ int llattn_attention_parts(llattn_ctx* ctx, const llattn_plan* plan, const llatt
  * copies out, on `stream`. The KV cache stays on the device, as in the reference engine. */
 int llattn_attention_host(llattn_ctx* ctx, const llattn_plan* plan, const llattn_io* io_host, void* stream);
 
+/* ---- attention without any allocation, for callers that cannot allocate device memory.
+ * No counterpart in the reference. Some hosts of this library may not call cudaMalloc at the point where they need
+ * attention: an engine whose memory plan is fixed at start-up and audited (every device byte accounted for before the
+ * first request), a plugin running inside another runtime's allocator, or code that has already entered a region
+ * where allocation is forbidden. This entry point serves them: it takes one sequence (the shape of the reference
+ * engine's layer step, engine/engine.cu:429-432 and :594-598: nb query blocks, block j seeing nblocks + j records of
+ * `cache` plus its own fresh K/V) and keeps its partial results in an array built into the library image instead of
+ * in allocated memory. It creates no context and no plan and calls no allocating routine.
+ *   Limits: nb <= 16 query blocks per call; the built-in array is 160 partial slots = 10.16 MiB, held by every GPU
+ *   that loads the library until the process exits. Larger requests are refused with LLATTN_EINVAL / LLATTN_ENOMEM.
+ *   First call on a device: resolves the array's device address and raises the kernel's shared-memory limit; make
+ *   that first call before any stream capture begins.
+ *   Sharing: every call on a device uses the same array. Calls whose kernels can overlap on the GPU (different
+ *   streams, or concurrent host threads) race on it; issue them on one stream or order them yourself.
+ * Outputs as in llattn_io (any of O16, O32, LSE, q8+s8+sum8; at least one). scale 0 means 1/sqrt(128). err_word: device
+ * int the kernel ORs an error code into if a bounded wait runs out (may be NULL). */
+int llattn_attention_static(const void* Q, const void* Kf, const void* Vf, const void* cache, int max_blocks, int nblocks,
+                            int nb, float scale, void* O16, float* O32, float* LSE, int8_t* q8, float* s8, int32_t* sum8,
+                            int* err_word, void* stream);
+
 /* Reads (and clears) the context's device error word; synchronises `stream`. 0 = no kernel wait ran out. */
 int llattn_device_status(llattn_ctx* ctx, void* stream, int* code);
 

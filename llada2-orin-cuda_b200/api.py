@@ -26,7 +26,7 @@ EXPORTS = (
     "llattn_version", "llattn_last_error", "llattn_pick_bpc", "llattn_chunks_for", "llattn_kv_commit",
     "llattn_kv_commit_paged", "llattn_attn_partial", "llattn_attn_combine", "llattn_create", "llattn_destroy",
     "llattn_plan_create", "llattn_plan_destroy", "llattn_plan_get_stats", "llattn_plan_preview", "llattn_attention",
-    "llattn_attention_parts", "llattn_attention_host", "llattn_device_status",
+    "llattn_attention_parts", "llattn_attention_host", "llattn_device_status", "llattn_attention_static",
 )
 
 
@@ -88,6 +88,8 @@ def lib() -> ctypes.CDLL:
         L.llattn_attention_parts.argtypes = [c_void_p, c_void_p, POINTER(_IO), c_int, c_void_p]
         L.llattn_attention_host.argtypes = [c_void_p, c_void_p, POINTER(_IO), c_void_p]
         L.llattn_device_status.argtypes = [c_void_p, c_void_p, POINTER(c_int)]
+        L.llattn_attention_static.argtypes = [c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_float,
+                                              c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p]
         _lib = L
     return _lib
 
@@ -173,6 +175,18 @@ def attn_combine(Opart, Mpart, Lpart, nchunks: int, nblocks: int, bpc: int, O=No
     """attn::attn_combine<<<dim3(4, 16, nb), 256>>>(...) (engine/attn.cu:319)."""
     _check(lib().llattn_attn_combine(_ptr(Opart), _ptr(Mpart), _ptr(Lpart), nchunks, nblocks, bpc, _ptr(O), _ptr(q8),
                                      _ptr(s8), _ptr(sum8), nb, _stream(stream)))
+
+
+def attention_static(Q, Kf, Vf, cache, max_blocks: int, nblocks: int, O16=None, O32=None, LSE=None, q8=None, s8=None,
+                     sum8=None, scale: float = 0.0, err_word=None, stream=None) -> None:
+    """One sequence's attention with no device allocation anywhere in the call: partial results live in an array built
+    into the library (10.16 MiB per GPU, shared by every call on that GPU, so calls that may overlap on the GPU race).
+    For hosts that must not allocate: a fixed, audited memory plan, a foreign runtime's allocator, a no-allocation
+    region. At most 16 query blocks (Q.shape[0]) per call; make the first call on a device before stream capture."""
+    nb = Q.shape[0]
+    _check(lib().llattn_attention_static(_ptr(Q), _ptr(Kf), _ptr(Vf), _ptr(cache), max_blocks, nblocks, nb, scale,
+                                         _ptr(O16), _ptr(O32), _ptr(LSE), _ptr(q8), _ptr(s8), _ptr(sum8), _ptr(err_word),
+                                         _stream(stream)))
 
 
 # ------------------------------------------------------------------ batched path

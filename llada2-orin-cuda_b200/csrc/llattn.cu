@@ -142,3 +142,87 @@ int llattn_kv_commit_paged(const void* Kf, const void* Vf, void* pool, const int
 }  // extern "C"
 
 #include "llattn_attention.inl"
+
+// ====================================================================================================== no-allocation entry point
+// Scratch for llattn_attention_static: partial results (un-normalised O, reference maximum, row sum) of up to
+// STATIC_MAX_SLOTS runs. It lives in the library image, so every GPU that loads the library holds these bytes until the
+// process exits, and every call on a device shares them.
+namespace {
+constexpr int STATIC_MAX_SLOTS = 160;                                  // 148 SMs worth of runs for one query block, rounded up
+constexpr int STATIC_MAX_QBLOCKS = 16;                                 // a prefill pass of the reference engine
+constexpr size_t STATIC_SLOT_FLOATS = size_t(llattn::QR) * llattn::D + 2 * llattn::QR;   // 16640 floats = 66560 B
+}  // namespace
+static __device__ __align__(256) float g_static_scratch[STATIC_MAX_SLOTS * STATIC_SLOT_FLOATS];   // 10.16 MiB
+
+namespace {
+struct StaticSetup { float* scratch = nullptr; int num_sms = 0; bool ready = false; };
+StaticSetup g_static[64];
+std::mutex g_static_mu;
+
+// Once per device, with that device current: resolve the DEVICE address of the scratch array. In host code the
+// array's name is only a stand-in symbol; handing it to a kernel would make the kernel dereference a host address.
+int static_setup(int dev, StaticSetup** out) {
+    if (dev < 0 || dev >= 64) return fail(LLATTN_EINVAL, "attention_static: device index %d not supported", dev);
+    std::lock_guard<std::mutex> lk(g_static_mu);
+    StaticSetup& st = g_static[dev];
+    if (!st.ready) {
+        float* ptr = nullptr;
+        cudaError_t e = cudaGetSymbolAddress(reinterpret_cast<void**>(&ptr), g_static_scratch);
+        if (e != cudaSuccess || !ptr) return fail(LLATTN_ECUDA, "attention_static: cudaGetSymbolAddress: %s", cudaGetErrorString(e));
+        e = cudaDeviceGetAttribute(&st.num_sms, cudaDevAttrMultiProcessorCount, dev);
+        if (e != cudaSuccess) return fail(LLATTN_ECUDA, "attention_static: cudaDeviceGetAttribute: %s", cudaGetErrorString(e));
+        st.scratch = ptr;
+        st.ready = true;
+    }
+    *out = &st;
+    return LLATTN_OK;
+}
+}  // namespace
+
+extern "C" int llattn_attention_static(const void* Q, const void* Kf, const void* Vf, const void* cache, int max_blocks,
+                                       int nblocks, int nb, float scale, void* O16, float* O32, float* LSE, int8_t* q8,
+                                       float* s8, int32_t* sum8, int* err_word, void* stream) {
+    using namespace llattn;
+    if (!Q || !Kf || !Vf) return fail(LLATTN_EINVAL, "attention_static: Q, Kf and Vf are required");
+    if (!O16 && !O32 && !LSE && !q8) return fail(LLATTN_EINVAL, "attention_static: no output requested");
+    if (q8 && (!s8 || !sum8)) return fail(LLATTN_EINVAL, "attention_static: q8 needs s8 and sum8");
+    if (nb < 1 || nb > STATIC_MAX_QBLOCKS)
+        return fail(LLATTN_EINVAL, "attention_static: %d query blocks; the built-in scratch serves 1..%d per call", nb, STATIC_MAX_QBLOCKS);
+    if (nblocks < 0 || max_blocks < 0 || nblocks + nb - 1 > max_blocks)
+        return fail(LLATTN_EINVAL, "attention_static: %d blocks visible, cache holds %d", nblocks + nb - 1, max_blocks);
+    if (nblocks + nb - 1 > 0 && !cache) return fail(LLATTN_EINVAL, "attention_static: null cache with committed blocks");
+    if (!aligned16(Q) || !aligned16(Kf) || !aligned16(Vf) || !aligned16(cache) || !aligned16(O16) || !aligned16(O32))
+        return fail(LLATTN_EINVAL, "attention_static: pointers must be 16-byte aligned");
+    int dev = -1;
+    CU(cudaGetDevice(&dev));
+    StaticSetup* st = nullptr;
+    if (int rc = static_setup(dev, &st)) return rc;
+    if (int rc = ensure_kernel_attrs()) return rc;
+    // split each (query block, kv head) into runs so that about one run lands on every SM, within the scratch's slots
+    const int nbl = nblocks + nb - 1;
+    const int want = std::max(1, std::min(STATIC_MAX_SLOTS / (NKV * nb), (st->num_sms + NKV * nb - 1) / (NKV * nb)));
+    int bpc = std::max(1, (nbl + want - 1) / want);
+    bpc = std::max(bpc, std::min(nbl, 8));                       // at least two 128-key tiles per run when there are that many
+    bpc = (bpc + TILE_UNITS - 1) / TILE_UNITS * TILE_UNITS;      // cuts on tile boundaries
+    const int nchunks = llattn_chunks_for(nbl, bpc);
+    if (NKV * nchunks * nb > STATIC_MAX_SLOTS)
+        return fail(LLATTN_ENOMEM, "attention_static: %d partial slots needed, the built-in scratch holds %d", NKV * nchunks * nb, STATIC_MAX_SLOTS);
+    const size_t ns = size_t(NKV) * nchunks * nb;
+    float* Opart = st->scratch;
+    float* Mpart = Opart + ns * QR * D;
+    float* Lpart = Mpart + ns * QR;
+    KParams p{};
+    p.Q = static_cast<const half*>(Q); p.Kf = static_cast<const half*>(Kf); p.Vf = static_cast<const half*>(Vf);
+    p.Opart = Opart; p.Mpart = Mpart; p.Lpart = Lpart;
+    p.sl2 = (scale > 0.f ? scale : 0.08838834764831845f) * 1.4426950408889634f;
+    p.err = err_word;
+    p.ref_seq = SeqDesc{static_cast<const uint8_t*>(cache), nullptr, max_blocks, nblocks, nb, 0};
+    p.ref_bpc = bpc;
+    p.ref_nchunks = nchunks;
+    attn_tile_kernel<<<NKV * nchunks * nb, ATTN_THREADS, ATTN_SMEM_BYTES, as_stream(stream)>>>(p);
+    CU(cudaGetLastError());
+    MergeOut o{static_cast<half*>(O16), O32, LSE, q8, s8, sum8};
+    combine_ref_kernel<<<dim3(NKV, QR / MERGE_ROWS, nb), MERGE_THREADS, 0, as_stream(stream)>>>(Opart, Mpart, Lpart, nchunks, nblocks, bpc, o);
+    CU(cudaGetLastError());
+    return LLATTN_OK;
+}

@@ -49,6 +49,7 @@ def test_argument_errors_are_status_codes_without_a_gpu(api):
     assert L.llattn_kv_commit(a + 2, a, a, 4, 0, 1, None) == api.EINVAL      # misaligned
     assert L.llattn_kv_commit(a, a, a, 4, 0, 0, None) == api.OK              # nothing to do
     assert L.llattn_attn_combine(None, None, None, 1, 0, 1, None, None, None, None, 1, None) == api.EINVAL
+    assert L.llattn_attention_static(a, a, a, a, 8, 4, 17, 0.0, a, None, None, None, None, None, None, None) == api.EINVAL
     assert L.llattn_plan_get_stats(None, None) == api.EINVAL
     st = api.PlanStats()
     assert L.llattn_plan_preview(None, 1, 1, ctypes.byref(st), None, 0, None, 0) == api.EINVAL
