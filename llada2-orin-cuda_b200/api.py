@@ -14,7 +14,7 @@ from dataclasses import dataclass
 from typing import Optional, Sequence
 
 HERE = os.path.dirname(os.path.abspath(__file__))
-LIB_PATH = os.path.join(HERE, "libllattn.so")
+LIB_PATH = os.environ.get("LLATTN_LIB", os.path.join(HERE, "libllattn.so"))   # LLATTN_LIB: another build of the same library
 
 D, BLK, NKV, NQH = 128, 32, 4, 16
 KV_BLOCK_BYTES, KOFF_META, VOFF, VOFF_META = 4736, 2048, 2560, 4608

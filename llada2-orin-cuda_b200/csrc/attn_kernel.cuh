@@ -22,7 +22,9 @@
 // each of up to 128 rows (query rows or keys), the 16 bytes of channels 8j..8j+7 at row*16. Within each group of 8
 // channels the order is (0,4,1,5,2,6,3,7): that is what the shift-free nibble unpack produces, Q and the fresh K are
 // stored in the same order (a dot product does not care) and V's order is undone when O is written out.
-// CS = 128*16 + 16: the 16-byte pad makes the 16-byte stores of one warp hit distinct banks.
+// CS = 128*16: a core matrix (8 rows x 16 bytes) is then 128-byte aligned, which the tensor core needs to fetch it in
+// one shared-memory wavefront (a padded stride halves the MMA rate). Threads therefore store so that the 8 lanes of a
+// quarter warp cover 8 different rows: their 16-byte stores land in distinct banks without padding.
 //
 // Every wait is bounded (ptx::mbar_wait); a wait that runs out sets a bit in the error word and every role leaves.
 #pragma once
@@ -32,11 +34,28 @@
 
 namespace llattn {
 
+// Timeline hooks for kernel tuning: compiled out unless LLATTN_TRACE is defined (the shipped library never defines it).
+#ifdef LLATTN_TRACE
+__device__ unsigned long long* g_trace_buf;      // [warps][LLATTN_TRACE_EVENTS] of (clock << 24 | tile << 8 | event)
+constexpr int LLATTN_TRACE_EVENTS = 2048;
+#define LLATTN_TR(ev, tile)                                                                                    \
+    do {                                                                                                       \
+        if (trace_ptr && trace_n < LLATTN_TRACE_EVENTS)                                                        \
+            trace_ptr[trace_n++] =                                 \
+                (static_cast<unsigned long long>(clock64()) << 24) | (static_cast<unsigned long long>((tile) & 0xffff) << 8) | (ev); \
+    } while (0)
+#else
+#define LLATTN_TR(ev, tile) do {} while (0)
+#endif
+#ifndef LLATTN_SKIP
+#define LLATTN_SKIP 0      // tuning builds only: 1 = no dequant arithmetic, 2 = no softmax arithmetic (results are garbage)
+#endif
+
 constexpr int TILE_UNITS = 4;
-constexpr int CS = 128 * 16 + 16;                  // chunk-row stride, bytes
-constexpr int TILE_BYTES = 16 * CS;                // 33024: Q or K tile
+constexpr int CS = 128 * 16;                       // chunk-row stride, bytes: every 8-row core matrix is 128-byte aligned
+constexpr int TILE_BYTES = 16 * CS;                // 32768: Q or K tile
 constexpr int V_ROWS = 18;                         // 16 chunk rows of dims + one holding the ones column + one of zeros
-constexpr int VTILE_BYTES = V_ROWS * CS;           // 37152
+constexpr int VTILE_BYTES = V_ROWS * CS;           // 36864
 constexpr int PV_N = 144;                          // dims 0..127, column 128 = row sum, 129..143 unused
 constexpr int NRAW = 8;                            // records in flight (two tiles' worth)
 constexpr int RAW_STRIDE = 4864;                   // 4736 rounded up to a multiple of 128
@@ -46,13 +65,16 @@ constexpr int SM_V = SM_K + 2 * TILE_BYTES;        // two V tiles
 constexpr int SM_RAW = SM_V + 2 * VTILE_BYTES;
 constexpr int SM_BAR = SM_RAW + NRAW * RAW_STRIDE;
 constexpr int SM_X = SM_BAR + 512;                 // row-max exchange between the two softmax warps of a lane quarter
-constexpr int SM_MISC = SM_X + 2 * 2 * 128 * 4;
+constexpr int SM_MISC = SM_X + 2 * 4 * 128 * 4;
 constexpr int ATTN_SMEM_BYTES = SM_MISC + 16;
-// warps 0-7 softmax (warp w: TMEM lane quarter w % 4, key half w / 4), 8-15 dequant (two groups of four, group g takes
-// the units u of a tile with u % 2 == g), 16 producer, 17 MMA
-constexpr int SOFTMAX_WARPS = 8, DEQUANT_WARPS = 8;
-constexpr int WARP_PRODUCER = SOFTMAX_WARPS + DEQUANT_WARPS, WARP_MMA = WARP_PRODUCER + 1;
-constexpr int ATTN_THREADS = 32 * (WARP_MMA + 1);  // 576
+// warps 0-7 softmax (warp w: TMEM lane quarter w % 4, key half w / 4), 8-23 dequant (four groups of four warps, group g
+// takes unit g of every tile), 24 producer, 25 S-MMA issue, 26 PV-MMA issue
+#ifndef LLATTN_DEQUANT_WARPS
+#define LLATTN_DEQUANT_WARPS 16
+#endif
+constexpr int SOFTMAX_WARPS = 8, DEQUANT_WARPS = LLATTN_DEQUANT_WARPS, DEQUANT_GROUPS = DEQUANT_WARPS / 4;
+constexpr int WARP_PRODUCER = SOFTMAX_WARPS + DEQUANT_WARPS, WARP_MMA = WARP_PRODUCER + 1, WARP_MMA_PV = WARP_MMA + 1;
+constexpr int ATTN_THREADS = 32 * (WARP_MMA_PV + 1);  // 864
 constexpr int TMEM_COLS = 512;
 constexpr int TM_S = 0, TM_O = 256, TM_L = TM_O + 128;   // S buffers at columns 0 and 128, O at 256..383, row sum at 384
 constexpr float RESCALE_SLACK = 8.f;
@@ -60,7 +82,7 @@ constexpr float RESCALE_SLACK = 8.f;
 // barrier indices
 enum { B_RAW_FULL = 0, B_RAW_EMPTY = B_RAW_FULL + NRAW, B_K_FULL = B_RAW_EMPTY + NRAW, B_V_FULL = B_K_FULL + 2,
        B_K_FREE = B_V_FULL + 2, B_PV_DONE = B_K_FREE + 2, B_S_FULL = B_PV_DONE + 2, B_P_FULL = B_S_FULL + 2,
-       B_Q_FULL = B_P_FULL + 2, B_O_FREE, B_SPARE, B_XCHG, B_COUNT = B_XCHG + 4 };
+       B_Q_FULL = B_P_FULL + 2, B_O_FREE, B_SPARE, B_XCHG = B_SPARE + 2, B_COUNT = B_XCHG + 4 };
 static_assert(B_COUNT * 8 <= 512, "barrier area");
 static_assert(ATTN_SMEM_BYTES <= 232448, "shared memory budget");
 
@@ -141,10 +163,11 @@ __device__ __forceinline__ float max3(float a, float b, float c) {
     return d;
 }
 
-// K half of one staged record -> fp16 at key offset (unit * 32) of a K tile. dt = 0..127: chunk row c = dt & 15,
-// tokens (dt >> 4) + 8 i.
+// K half of one staged record -> fp16 at key offset (unit * 32) of a K tile. dt = 0..127: chunk row c = dt >> 3,
+// tokens (dt & 7) + 8 i: a quarter warp stores 8 different tokens of one chunk row (distinct banks); its 4-byte code
+// loads fall on two banks (4 wavefronts, the same as one 16-byte store).
 __device__ __forceinline__ void dequant_k(const uint8_t* raw, uint8_t* Kt, int dt) {
-    const int c = dt & 15, tb = dt >> 4;
+    const int c = dt >> 3, tb = dt & 7;
     const uint4 s4 = permute8(*reinterpret_cast<const uint4*>(raw + KOFF_META + c * 16));
     const uint4 m4 = permute8(*reinterpret_cast<const uint4*>(raw + KOFF_META + 256 + c * 16));
     const half2* ks = reinterpret_cast<const half2*>(&s4);
@@ -161,7 +184,7 @@ __device__ __forceinline__ void dequant_k(const uint8_t* raw, uint8_t* Kt, int d
 }
 // V half: scale and min per token.
 __device__ __forceinline__ void dequant_v(const uint8_t* raw, uint8_t* Vt, int dt) {
-    const int c = dt & 15, tb = dt >> 4;
+    const int c = dt >> 3, tb = dt & 7;
     const half* vmeta = reinterpret_cast<const half*>(raw + VOFF_META);
 #pragma unroll
     for (int i = 0; i < 4; ++i) {
@@ -199,6 +222,7 @@ __device__ __forceinline__ void attn_tile_body(const KParams& p, const int cta) 
         }
         ptx::mbar_init(BAR(B_Q_FULL), 32 * DEQUANT_WARPS); ptx::mbar_init(BAR(B_O_FREE), 32 * SOFTMAX_WARPS);
         ptx::mbar_init(BAR(B_SPARE), 1);
+        ptx::mbar_init(BAR(B_SPARE + 1), 1);
         for (int i = 0; i < 4; ++i) ptx::mbar_init(BAR(B_XCHG + i), 64);
         ptx::fence_mbar_init();
         *abort_flag = 0;
@@ -209,6 +233,10 @@ __device__ __forceinline__ void attn_tile_body(const KParams& p, const int cta) 
     ptx::tc_fence_after();
     const uint32_t tmem = *tmem_slot;
     int errbits = 0;
+#ifdef LLATTN_TRACE
+    int trace_n = 0;
+    unsigned long long* trace_ptr = (blockIdx.x == 0 && lane == 0 && g_trace_buf) ? g_trace_buf + warp * LLATTN_TRACE_EVENTS : nullptr;
+#endif
 
     if (warp < SOFTMAX_WARPS) {
         // ================================================================== softmax + epilogue
@@ -325,14 +353,14 @@ __device__ __forceinline__ void attn_tile_body(const KParams& p, const int cta) 
         }
     } else if (warp < WARP_PRODUCER) {
         // ================================================================== dequant: records -> fp16 operand tiles
-        const int da = tid - 32 * SOFTMAX_WARPS;      // 0..255 over both groups
-        const int grp = da >> 7, dt = da & 127;       // group g owns the units u of a tile with u % 2 == g
+        const int da = tid - 32 * SOFTMAX_WARPS;      // 0..511 over the four groups
+        const int grp = da >> 7, dt = da & 127;       // group g owns unit g of every tile
         uint32_t t = 0, r = 0;
         int prev_last = -1;
         bool alive = true;
         // chunk row 16 of both V tiles: (1, 0, 0, 0, 0, 0, 0, 0) for every key -> O column 128 accumulates sum(P);
         // chunk row 17: zeros. Published by the first v_full arrival.
-        for (int idx = da; idx < 2 * 2 * 128; idx += 256) {
+        for (int idx = da; idx < 2 * 2 * 128; idx += 32 * DEQUANT_WARPS) {
             const int buf = idx >> 8, rw = (idx >> 7) & 1, key = idx & 127;
             *reinterpret_cast<uint4*>(smem + SM_V + buf * VTILE_BYTES + (16 + rw) * CS + key * 16) =
                 make_uint4(rw == 0 ? 0x00003C00u : 0u, 0u, 0u, 0u);
@@ -346,9 +374,9 @@ __device__ __forceinline__ void attn_tile_body(const KParams& p, const int cta) 
             const size_t f0 = (qg * BLK) * NKV * D + size_t(w.kvh) * D;
             if (prev_last >= 0 &&      // Q is overwritten: every S MMA of the previous item must be done
                 !ptx::mbar_wait(BAR(B_K_FREE + (prev_last & 1)), (uint32_t(prev_last) >> 1) & 1, abort_flag)) { alive = false; errbits |= ERR_WAIT_DEQUANT; break; }
-#pragma unroll 4
-            for (int i = 0; i < 8; ++i) {
-                const int idx = da + 256 * i, rw = idx >> 4, ch = idx & 15;
+#pragma unroll
+            for (int i = 0; i < 2048 / (32 * DEQUANT_WARPS); ++i) {
+                const int idx = da + 32 * DEQUANT_WARPS * i, rw = (idx & 7) | ((idx >> 7) << 3), ch = (idx >> 3) & 15;
                 const half* src = p.Q + ((qg * BLK + (rw >> 2)) * NQH + 4 * w.kvh + (rw & 3)) * D + ch * 8;
                 *reinterpret_cast<uint4*>(smem + SM_Q + ch * CS + rw * 16) = permute8(__ldg(reinterpret_cast<const uint4*>(src)));
             }
@@ -360,18 +388,22 @@ __device__ __forceinline__ void attn_tile_body(const KParams& p, const int cta) 
                 uint8_t* Kt = smem + SM_K + b * TILE_BYTES;
                 uint8_t* Vt = smem + SM_V + b * VTILE_BYTES;
                 // ---- K: the tile's K buffer is free once S of tile t-2 has been computed
+                LLATTN_TR(10, t);
                 if (t >= 2 && !ptx::mbar_wait(BAR(B_K_FREE + b), ((t >> 1) - 1) & 1, abort_flag)) { alive = false; errbits |= ERR_WAIT_DEQUANT; break; }
+                LLATTN_TR(11, t);
 #pragma unroll 1
-                for (int u = grp; u < nu; u += 2) {
+                for (int u = grp; u < nu; u += DEQUANT_GROUPS) {
                     const int unit = TILE_UNITS * i + u;
                     if (unit < w.rec_count) {
                         const uint32_t rr = r + u, slot = rr % NRAW;
+                        LLATTN_TR(15, t);
                         if (!ptx::mbar_wait(BAR(B_RAW_FULL + slot), (rr / NRAW) & 1, abort_flag)) { alive = false; errbits |= ERR_WAIT_DEQUANT; break; }
-                        dequant_k(smem + SM_RAW + slot * RAW_STRIDE, Kt + u * 512, dt);
+                        LLATTN_TR(16, t);
+                        if (!(LLATTN_SKIP & 1)) dequant_k(smem + SM_RAW + slot * RAW_STRIDE, Kt + u * 512, dt);
                     } else {          // the query block's own K, exact fp16
 #pragma unroll
                         for (int k = 0; k < 4; ++k) {
-                            const int idx = dt + 128 * k, tok = idx >> 4, ch = idx & 15;
+                            const int idx = dt + 128 * k, tok = (idx & 7) | ((idx >> 7) << 3), ch = (idx >> 3) & 15;
                             *reinterpret_cast<uint4*>(Kt + u * 512 + ch * CS + tok * 16) =
                                 permute8(__ldg(reinterpret_cast<const uint4*>(p.Kf + f0 + size_t(tok) * NKV * D + ch * 8)));
                         }
@@ -380,19 +412,21 @@ __device__ __forceinline__ void attn_tile_body(const KParams& p, const int cta) 
                 if (!alive) break;
                 ptx::fence_proxy_async_smem();
                 ptx::mbar_arrive(BAR(B_K_FULL + b));
+                LLATTN_TR(12, t);
                 // ---- V: free once PV of tile t-2 has been computed
                 if (t >= 2 && !ptx::mbar_wait(BAR(B_PV_DONE + b), ((t >> 1) - 1) & 1, abort_flag)) { alive = false; errbits |= ERR_WAIT_DEQUANT; break; }
+                LLATTN_TR(13, t);
 #pragma unroll 1
-                for (int u = grp; u < nu; u += 2) {
+                for (int u = grp; u < nu; u += DEQUANT_GROUPS) {
                     const int unit = TILE_UNITS * i + u;
                     if (unit < w.rec_count) {
                         const uint32_t slot = (r + u) % NRAW;       // landed: the K pass waited for it
-                        dequant_v(smem + SM_RAW + slot * RAW_STRIDE, Vt + u * 512, dt);
+                        if (!(LLATTN_SKIP & 1)) dequant_v(smem + SM_RAW + slot * RAW_STRIDE, Vt + u * 512, dt);
                         ptx::mbar_arrive(BAR(B_RAW_EMPTY + slot));
                     } else {
 #pragma unroll
                         for (int k = 0; k < 4; ++k) {
-                            const int idx = dt + 128 * k, tok = idx >> 4, ch = idx & 15;
+                            const int idx = dt + 128 * k, tok = (idx & 7) | ((idx >> 7) << 3), ch = (idx >> 3) & 15;
                             *reinterpret_cast<uint4*>(Vt + u * 512 + ch * CS + tok * 16) =
                                 permute8(__ldg(reinterpret_cast<const uint4*>(p.Vf + f0 + size_t(tok) * NKV * D + ch * 8)));
                         }
@@ -400,6 +434,7 @@ __device__ __forceinline__ void attn_tile_body(const KParams& p, const int cta) 
                 }
                 ptx::fence_proxy_async_smem();
                 ptx::mbar_arrive(BAR(B_V_FULL + b));
+                LLATTN_TR(14, t);
                 r += uint32_t(min(nu, max(0, w.rec_count - TILE_UNITS * i)));     // records of this tile (both groups count alike)
             }
             prev_last = int(t) - 1;
@@ -435,63 +470,98 @@ __device__ __forceinline__ void attn_tile_body(const KParams& p, const int cta) 
                 ptx::mbar_wait(BAR(B_RAW_FULL + rr % NRAW), (rr / NRAW) & 1, &never);
             }
         }
-    } else {
-        // ================================================================== MMA issue (lane 0 issues, the warp stays together)
+    } else if (warp == WARP_MMA) {
+        // ================================================================== S = Q K^T issue (lane 0 issues, the warp stays together)
+        // Two issuing warps (this one and the PV one below) halve the per-tile instruction chain on the critical path.
+        // Every descriptor is built once: the operands' shared-memory addresses never change.
         uint32_t t = 0, itc = 0;
         bool alive = true;
-        const uint32_t q_s = ptx::smem_u32(smem + SM_Q), k_s = ptx::smem_u32(smem + SM_K), v_s = ptx::smem_u32(smem + SM_V);
-        const uint32_t idO = ptx::idesc_f16(128, PV_N, false, true);
-        auto issue_pv = [&](uint32_t tt, int nu, bool first) -> bool {
-            const uint32_t bb = tt & 1;
-            if (!ptx::mbar_wait(BAR(B_V_FULL + bb), (tt >> 1) & 1, abort_flag)) return false;
-            if (!ptx::mbar_wait(BAR(B_P_FULL + bb), (tt >> 1) & 1, abort_flag)) return false;
-            if (first && itc > 0 && !ptx::mbar_wait(BAR(B_O_FREE), (itc - 1) & 1, abort_flag)) return false;
-            ptx::tc_fence_after();
-            if (lane == 0) {
-                for (int j = 0; j < 2 * nu; ++j)   // 16 keys per step: B is MN-major, 8-key groups 128 B apart, dim groups CS apart
-                    ptx::mma_ts(tmem + TM_O, tmem + TM_S + bb * 128 + (j >> 2) * 64 + (j & 3) * 8,
-                                ptx::smem_desc(v_s + bb * VTILE_BYTES + j * 256, 128, CS), idO, (first && j == 0) ? 0u : 1u);
-                ptx::mma_commit(BAR(B_PV_DONE + bb));
-            }
-            __syncwarp();
-            return true;
-        };
+        const uint32_t q_s = ptx::smem_u32(smem + SM_Q), k_s = ptx::smem_u32(smem + SM_K);
+        uint64_t qd[8], kd[2][8];        // 16 channels per K-step: K-major, chunk rows CS apart, 8-row groups 128 B apart
+#pragma unroll
+        for (int j = 0; j < 8; ++j) {
+            qd[j] = ptx::smem_desc(q_s + 2 * j * CS, CS, 128);
+            kd[0][j] = ptx::smem_desc(k_s + 2 * j * CS, CS, 128);
+            kd[1][j] = ptx::smem_desc(k_s + TILE_BYTES + 2 * j * CS, CS, 128);
+        }
 #pragma unroll 1
         for (int ii = i0; ii < i1 && alive; ++ii) {
             WorkItem w; SeqDesc s;
             if (!fetch_item(p, ii, w, s)) continue;
             const int U = w.rec_count + w.fresh, ntiles = (U + TILE_UNITS - 1) / TILE_UNITS;
             if (!ptx::mbar_wait(BAR(B_Q_FULL), itc & 1, abort_flag)) { alive = false; errbits |= ERR_WAIT_MMA; break; }
-            int nu_prev = 0;
 #pragma unroll 1
             for (int i = 0; i < ntiles; ++i, ++t) {
                 const uint32_t b = t & 1;
                 const int nu = min(TILE_UNITS, U - TILE_UNITS * i);
+                LLATTN_TR(20, t);
                 if (!ptx::mbar_wait(BAR(B_K_FULL + b), (t >> 1) & 1, abort_flag)) { alive = false; errbits |= ERR_WAIT_MMA; break; }
+                // S buffer b also holds P of tile t-2: PV of that tile must have consumed it
+                if (t >= 2 && !ptx::mbar_wait(BAR(B_PV_DONE + b), ((t >> 1) - 1) & 1, abort_flag)) { alive = false; errbits |= ERR_WAIT_MMA; break; }
+                LLATTN_TR(21, t);
                 ptx::tc_fence_after();
-                if (lane == 0) {
-                    const uint32_t idS = ptx::idesc_f16(128, 32 * nu, false, false);
-#pragma unroll
-                    for (int j = 0; j < 8; ++j)    // 16 channels per step: both operands K-major, chunk rows CS apart, 8-row groups 128 B apart
-                        ptx::mma_ss(tmem + TM_S + b * 128, ptx::smem_desc(q_s + 2 * j * CS, CS, 128),
-                                    ptx::smem_desc(k_s + b * TILE_BYTES + 2 * j * CS, CS, 128), idS, j > 0 ? 1u : 0u);
-                    ptx::mma_commit(BAR(B_S_FULL + b));
-                    ptx::mma_commit(BAR(B_K_FREE + b));
+                {
+                    const uint32_t idS = ptx::idesc_f16(128, 32 * nu, false, false), ds = tmem + TM_S + b * 128;
+                    if (b == 0) ptx::mma_ss_x8_warp(ds, qd, kd[0], idS, BAR(B_S_FULL), BAR(B_K_FREE));
+                    else ptx::mma_ss_x8_warp(ds, qd, kd[1], idS, BAR(B_S_FULL + 1), BAR(B_K_FREE + 1));
                 }
-                __syncwarp();
-                if (i > 0 && !issue_pv(t - 1, nu_prev, i == 1)) { alive = false; errbits |= ERR_WAIT_MMA; break; }
-                nu_prev = nu;
+                LLATTN_TR(25, t);
             }
-            if (!alive) break;
-            if (!issue_pv(t - 1, nu_prev, ntiles == 1)) { alive = false; errbits |= ERR_WAIT_MMA; break; }
             ++itc;
         }
         // every MMA issued must have retired before tensor memory is released
-        if (lane == 0) ptx::mma_commit(BAR(B_SPARE));
-        __syncwarp();
+        ptx::mma_commit_warp(BAR(B_SPARE));
         {
             volatile int never = 0;
             if (!ptx::mbar_wait(BAR(B_SPARE), 0, &never)) errbits |= ERR_WAIT_TEARDOWN;
+        }
+    } else {
+        // ================================================================== O += P V issue
+        uint32_t t = 0, itc = 0;
+        bool alive = true;
+        const uint32_t v_s = ptx::smem_u32(smem + SM_V);
+        const uint32_t idO = ptx::idesc_f16(128, PV_N, false, true);
+        uint64_t vd[2][8];               // 16 keys per K-step: B is MN-major, 8-key groups 128 B apart, dim groups CS apart
+#pragma unroll
+        for (int j = 0; j < 8; ++j) {
+            vd[0][j] = ptx::smem_desc(v_s + j * 256, 128, CS);
+            vd[1][j] = ptx::smem_desc(v_s + VTILE_BYTES + j * 256, 128, CS);
+        }
+#pragma unroll 1
+        for (int ii = i0; ii < i1 && alive; ++ii) {
+            WorkItem w; SeqDesc s;
+            if (!fetch_item(p, ii, w, s)) continue;
+            const int U = w.rec_count + w.fresh, ntiles = (U + TILE_UNITS - 1) / TILE_UNITS;
+#pragma unroll 1
+            for (int i = 0; i < ntiles; ++i, ++t) {
+                const uint32_t b = t & 1;
+                const int nu = min(TILE_UNITS, U - TILE_UNITS * i);
+                LLATTN_TR(22, t);
+                if (!ptx::mbar_wait(BAR(B_V_FULL + b), (t >> 1) & 1, abort_flag)) { alive = false; errbits |= ERR_WAIT_MMA; break; }
+                LLATTN_TR(23, t);
+                if (!ptx::mbar_wait(BAR(B_P_FULL + b), (t >> 1) & 1, abort_flag)) { alive = false; errbits |= ERR_WAIT_MMA; break; }
+                LLATTN_TR(24, t);
+                // the previous item's epilogue must have read O before the first PV of this item overwrites it
+                if (i == 0 && itc > 0 && !ptx::mbar_wait(BAR(B_O_FREE), (itc - 1) & 1, abort_flag)) { alive = false; errbits |= ERR_WAIT_MMA; break; }
+                ptx::tc_fence_after();
+                {
+                    // unit u = keys 32u..32u+31 = K-steps 2u, 2u+1; its P sits at columns (u >> 1) * 64 + (u & 1) * 16 of the S buffer
+                    const uint32_t pb = tmem + TM_S + b * 128;
+#pragma unroll
+                    for (int u = 0; u < TILE_UNITS; ++u)
+                        if (u < nu)
+                            ptx::mma_ts_x2_warp(tmem + TM_O, pb + (u >> 1) * 64 + (u & 1) * 16, b ? vd[1][2 * u] : vd[0][2 * u],
+                                                b ? vd[1][2 * u + 1] : vd[0][2 * u + 1], idO, (i == 0 && u == 0) ? 0u : 1u);
+                    ptx::mma_commit_warp(BAR(B_PV_DONE + b));
+                }
+                LLATTN_TR(26, t);
+            }
+            ++itc;
+        }
+        ptx::mma_commit_warp(BAR(B_SPARE + 1));
+        {
+            volatile int never = 0;
+            if (!ptx::mbar_wait(BAR(B_SPARE + 1), 0, &never)) errbits |= ERR_WAIT_TEARDOWN;
         }
     }
 

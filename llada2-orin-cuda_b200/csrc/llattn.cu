@@ -226,3 +226,11 @@ extern "C" int llattn_attention_static(const void* Q, const void* Kf, const void
     CU(cudaGetLastError());
     return LLATTN_OK;
 }
+
+#ifdef LLATTN_TRACE
+// Tuning builds only: points the kernel's timeline hooks at a device buffer of 18 * 2048 64-bit words.
+extern "C" int llattn_debug_set_trace(void* dev_ptr) {
+    CU(cudaMemcpyToSymbol(llattn::g_trace_buf, &dev_ptr, sizeof(dev_ptr)));
+    return LLATTN_OK;
+}
+#endif

@@ -12,6 +12,8 @@ namespace llattn {
 namespace ptx {
 
 constexpr unsigned long long WAIT_LIMIT_NS = 2000000000ull;   // 2 s: far above any kernel's whole runtime
+constexpr uint32_t SUSPEND_HINT_NS = 20000;                   // a waiting thread may sleep this long in hardware; it is woken
+                                                              // when the phase completes, so polling costs no issue slots
 
 __device__ __forceinline__ uint32_t smem_u32(const void* p) { return static_cast<uint32_t>(__cvta_generic_to_shared(p)); }
 
@@ -54,8 +56,8 @@ __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatil
     unsigned long long t0 = 0;
     for (uint32_t it = 0;; ++it) {
         asm volatile(
-            "{\n\t.reg .pred p;\n\tmbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\tselp.b32 %0, 1, 0, p;\n\t}\n"
-            : "=r"(ok) : "r"(bar), "r"(parity) : "memory");
+            "{\n\t.reg .pred p;\n\tmbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2, %3;\n\tselp.b32 %0, 1, 0, p;\n\t}\n"
+            : "=r"(ok) : "r"(bar), "r"(parity), "r"(SUSPEND_HINT_NS) : "memory");
         if (ok) return true;
         if ((it & 63u) == 63u) {
             if (*abort_flag) return false;
@@ -164,6 +166,117 @@ __device__ __forceinline__ void mma_ts(uint32_t d_tmem, uint32_t a_tmem, uint64_
         "{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\t"
         "tcgen05.mma.cta_group::1.kind::f16 [%0], [%1], %2, %3, p;\n\t}\n"
         :: "r"(d_tmem), "r"(a_tmem), "l"(bdesc), "r"(idesc), "r"(accumulate) : "memory");
+}
+// Descriptor words for the fused issue helpers below: the low word carries the start address and LBO, the high word
+// SBO and the version bit; stepping an operand through shared memory is an add on the low word (16-byte units).
+__device__ __forceinline__ uint32_t desc_lo(uint32_t saddr, uint32_t lbo_bytes) {
+    return ((saddr & 0x3ffffu) >> 4) | ((lbo_bytes >> 4) << 16);
+}
+__host__ __device__ constexpr uint32_t desc_hi(uint32_t sbo_bytes) { return (sbo_bytes >> 4) | (1u << 14); }
+
+// Eight back-to-back K-steps of D[tmem] = A[smem] * B[smem] (first step overwrites D, the rest accumulate). Both
+// operands advance by `step16` 16-byte units per step. One asm block: a few instructions per MMA on the issuing thread.
+__device__ __forceinline__ void mma_ss_x8(uint32_t d_tmem, uint32_t alo, uint32_t ahi, uint32_t blo, uint32_t bhi,
+                                          uint32_t idesc, uint32_t step16) {
+    asm volatile(
+        "{\n\t"
+        ".reg .pred pf, pt;\n\t"
+        ".reg .b32 al, bl;\n\t"
+        ".reg .b64 da, db;\n\t"
+        "setp.ne.b32 pf, 0, 0;\n\t"
+        "setp.eq.b32 pt, 0, 0;\n\t"
+        "mov.b64 da, {%1, %2};\n\t"
+        "mov.b64 db, {%3, %4};\n\t"
+        "tcgen05.mma.cta_group::1.kind::f16 [%0], da, db, %5, pf;\n\t"
+        "add.u32 al, %1, %6;\n\t add.u32 bl, %3, %6;\n\t mov.b64 da, {al, %2};\n\t mov.b64 db, {bl, %4};\n\t"
+        "tcgen05.mma.cta_group::1.kind::f16 [%0], da, db, %5, pt;\n\t"
+        "add.u32 al, al, %6;\n\t add.u32 bl, bl, %6;\n\t mov.b64 da, {al, %2};\n\t mov.b64 db, {bl, %4};\n\t"
+        "tcgen05.mma.cta_group::1.kind::f16 [%0], da, db, %5, pt;\n\t"
+        "add.u32 al, al, %6;\n\t add.u32 bl, bl, %6;\n\t mov.b64 da, {al, %2};\n\t mov.b64 db, {bl, %4};\n\t"
+        "tcgen05.mma.cta_group::1.kind::f16 [%0], da, db, %5, pt;\n\t"
+        "add.u32 al, al, %6;\n\t add.u32 bl, bl, %6;\n\t mov.b64 da, {al, %2};\n\t mov.b64 db, {bl, %4};\n\t"
+        "tcgen05.mma.cta_group::1.kind::f16 [%0], da, db, %5, pt;\n\t"
+        "add.u32 al, al, %6;\n\t add.u32 bl, bl, %6;\n\t mov.b64 da, {al, %2};\n\t mov.b64 db, {bl, %4};\n\t"
+        "tcgen05.mma.cta_group::1.kind::f16 [%0], da, db, %5, pt;\n\t"
+        "add.u32 al, al, %6;\n\t add.u32 bl, bl, %6;\n\t mov.b64 da, {al, %2};\n\t mov.b64 db, {bl, %4};\n\t"
+        "tcgen05.mma.cta_group::1.kind::f16 [%0], da, db, %5, pt;\n\t"
+        "add.u32 al, al, %6;\n\t add.u32 bl, bl, %6;\n\t mov.b64 da, {al, %2};\n\t mov.b64 db, {bl, %4};\n\t"
+        "tcgen05.mma.cta_group::1.kind::f16 [%0], da, db, %5, pt;\n\t"
+        "}\n"
+        :: "r"(d_tmem), "r"(alo), "r"(ahi), "r"(blo), "r"(bhi), "r"(idesc), "r"(step16) : "memory");
+}
+// Two K-steps (32 keys = one KV unit) of D[tmem] (+)= A[tmem] * B[smem]: A advances 8 TMEM columns, B `step16` units.
+__device__ __forceinline__ void mma_ts_x2(uint32_t d_tmem, uint32_t a_tmem, uint32_t blo, uint32_t bhi, uint32_t idesc,
+                                          uint32_t step16, uint32_t accumulate_first) {
+    asm volatile(
+        "{\n\t"
+        ".reg .pred pa, pt;\n\t"
+        ".reg .b32 bl, at;\n\t"
+        ".reg .b64 db;\n\t"
+        "setp.ne.b32 pa, %6, 0;\n\t"
+        "setp.eq.b32 pt, 0, 0;\n\t"
+        "mov.b64 db, {%2, %3};\n\t"
+        "tcgen05.mma.cta_group::1.kind::f16 [%0], [%1], db, %4, pa;\n\t"
+        "add.u32 bl, %2, %5;\n\t add.u32 at, %1, 8;\n\t mov.b64 db, {bl, %3};\n\t"
+        "tcgen05.mma.cta_group::1.kind::f16 [%0], [at], db, %4, pt;\n\t"
+        "}\n"
+        :: "r"(d_tmem), "r"(a_tmem), "r"(blo), "r"(bhi), "r"(idesc), "r"(step16), "r"(accumulate_first) : "memory");
+}
+// Single MMAs with ready-made 64-bit descriptors and a compile-time accumulate flag: nothing but the predicate set-up
+// and the MMA itself on the issuing thread.
+template <bool kAccumulate>
+__device__ __forceinline__ void mma_ss_d(uint32_t d_tmem, uint64_t adesc, uint64_t bdesc, uint32_t idesc) {
+    if (kAccumulate)
+        asm volatile("{\n\t.reg .pred p;\n\tsetp.eq.b32 p, 0, 0;\n\ttcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n\t}\n"
+                     :: "r"(d_tmem), "l"(adesc), "l"(bdesc), "r"(idesc) : "memory");
+    else
+        asm volatile("{\n\t.reg .pred p;\n\tsetp.ne.b32 p, 0, 0;\n\ttcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n\t}\n"
+                     :: "r"(d_tmem), "l"(adesc), "l"(bdesc), "r"(idesc) : "memory");
+}
+__device__ __forceinline__ void mma_ts_d(uint32_t d_tmem, uint32_t a_tmem, uint64_t bdesc, uint32_t idesc, uint32_t accumulate) {
+    asm volatile("{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\ttcgen05.mma.cta_group::1.kind::f16 [%0], [%1], %2, %3, p;\n\t}\n"
+                 :: "r"(d_tmem), "r"(a_tmem), "l"(bdesc), "r"(idesc), "r"(accumulate) : "memory");
+}
+// Whole-warp issue helpers: every lane executes them (uniform control flow, so the operands can live in uniform
+// registers); one elected lane issues. Eight K-steps of D = A[smem] * B[smem] with ready-made descriptors, then the
+// commits that publish completion.
+__device__ __forceinline__ void mma_ss_x8_warp(uint32_t d_tmem, const uint64_t (&a)[8], const uint64_t (&b)[8], uint32_t idesc,
+                                               uint32_t bar1, uint32_t bar2) {
+    asm volatile(
+        "{\n\t.reg .pred pe, pf, pt;\n\t"
+        "elect.sync _|pe, 0xffffffff;\n\t"
+        "setp.ne.b32 pf, 0, 0;\n\t setp.eq.b32 pt, 0, 0;\n\t"
+        "@pe tcgen05.mma.cta_group::1.kind::f16 [%0], %2, %10, %1, pf;\n\t"
+        "@pe tcgen05.mma.cta_group::1.kind::f16 [%0], %3, %11, %1, pt;\n\t"
+        "@pe tcgen05.mma.cta_group::1.kind::f16 [%0], %4, %12, %1, pt;\n\t"
+        "@pe tcgen05.mma.cta_group::1.kind::f16 [%0], %5, %13, %1, pt;\n\t"
+        "@pe tcgen05.mma.cta_group::1.kind::f16 [%0], %6, %14, %1, pt;\n\t"
+        "@pe tcgen05.mma.cta_group::1.kind::f16 [%0], %7, %15, %1, pt;\n\t"
+        "@pe tcgen05.mma.cta_group::1.kind::f16 [%0], %8, %16, %1, pt;\n\t"
+        "@pe tcgen05.mma.cta_group::1.kind::f16 [%0], %9, %17, %1, pt;\n\t"
+        "@pe tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%18];\n\t"
+        "@pe tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%19];\n\t"
+        "}\n"
+        :: "r"(d_tmem), "r"(idesc), "l"(a[0]), "l"(a[1]), "l"(a[2]), "l"(a[3]), "l"(a[4]), "l"(a[5]), "l"(a[6]), "l"(a[7]),
+           "l"(b[0]), "l"(b[1]), "l"(b[2]), "l"(b[3]), "l"(b[4]), "l"(b[5]), "l"(b[6]), "l"(b[7]), "r"(bar1), "r"(bar2)
+        : "memory");
+}
+// Two K-steps (one 32-key unit) of D (+)= A[tmem] * B[smem]; A advances 8 TMEM columns.
+__device__ __forceinline__ void mma_ts_x2_warp(uint32_t d_tmem, uint32_t a_tmem, uint64_t b0, uint64_t b1, uint32_t idesc,
+                                               uint32_t accumulate_first) {
+    asm volatile(
+        "{\n\t.reg .pred pe, pa, pt;\n\t.reg .b32 at;\n\t"
+        "elect.sync _|pe, 0xffffffff;\n\t"
+        "setp.ne.b32 pa, %5, 0;\n\t setp.eq.b32 pt, 0, 0;\n\t"
+        "add.u32 at, %1, 8;\n\t"
+        "@pe tcgen05.mma.cta_group::1.kind::f16 [%0], [%1], %2, %4, pa;\n\t"
+        "@pe tcgen05.mma.cta_group::1.kind::f16 [%0], [at], %3, %4, pt;\n\t"
+        "}\n"
+        :: "r"(d_tmem), "r"(a_tmem), "l"(b0), "l"(b1), "r"(idesc), "r"(accumulate_first) : "memory");
+}
+__device__ __forceinline__ void mma_commit_warp(uint32_t bar) {
+    asm volatile("{\n\t.reg .pred pe;\n\telect.sync _|pe, 0xffffffff;\n\t"
+                 "@pe tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];\n\t}\n" ::"r"(bar) : "memory");
 }
 // Arrive once on `bar` when every MMA issued so far by this thread has completed.
 __device__ __forceinline__ void mma_commit(uint32_t bar) {
