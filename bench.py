@@ -37,6 +37,10 @@ sys.path.insert(0, ROOT)
 
 LAYERS = 20
 METRIC = "block-attn query tok/s @32K int4 KV"
+# DRAM bytes (read + write) the tile kernel moved per KV unit (one 4736-byte record, or the fresh block) in an ncu capture
+# of a 32-sequence, 1-layer launch: 643.3 MB over 131,200 units. Traffic grows in proportion to the units a launch
+# processes, so a launch's traffic is this figure times its units.
+NCU_TRAFFIC_BYTES_PER_UNIT = 643.3e6 / 131200
 
 
 def parse():
@@ -63,7 +67,7 @@ def peaks():
 
 
 class ClockSampler:
-    """Samples nvidia-smi clocks and throttle reasons every 200 ms while the timed region runs."""
+    """Samples nvidia-smi clocks and throttle reasons every 50 ms while the timed region runs."""
     Q = ("index,clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.active,clocks_event_reasons.hw_slowdown,"
          "clocks_event_reasons.hw_thermal_slowdown,clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
 
@@ -72,7 +76,7 @@ class ClockSampler:
 
     def start(self):
         try:
-            self.proc = subprocess.Popen(["nvidia-smi", f"--query-gpu={self.Q}", "--format=csv,noheader,nounits", "-lms", "200",
+            self.proc = subprocess.Popen(["nvidia-smi", f"--query-gpu={self.Q}", "--format=csv,noheader,nounits", "-lms", "50",
                                           "-i", str(self.index)], stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
             self.th = threading.Thread(target=self._read, daemon=True)
             self.th.start()
@@ -255,22 +259,29 @@ def run_ours(a):
     clocks = sampler.stop() if rank == 0 else None
     assert ctx.device_status(stream) == 0
 
-    # ---- per-kernel time of the tile kernel (events around that kernel alone, same stream, no graph)
-    k0, k1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-    with torch.cuda.stream(stream):
-        step(parts=1)
-        k0.record(stream)
-        for _ in range(a.steps):
-            step(parts=1)
-        k1.record(stream)
-        m0, m1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-        m0.record(stream)
-        for _ in range(a.steps):
-            step(parts=2)
-        m1.record(stream)
-    barrier()
-    tile_ms = k0.elapsed_time(k1) / (a.steps * L)
-    merge_ms = m0.elapsed_time(m1) / (a.steps * L)
+    # ---- per-kernel time: the 20 tile-kernel launches of a step alone (and the 20 merges alone), each set replayed as
+    # its own CUDA graph with events around the replays on the launch stream
+    def timed_parts(parts):
+        with torch.cuda.stream(stream):
+            step(parts=parts)
+            stream.synchronize()
+            g_ = None
+            if not a.no_graph:
+                g_ = torch.cuda.CUDAGraph()
+                with torch.cuda.graph(g_, stream=stream):
+                    step(parts=parts)
+            go = (lambda: g_.replay()) if g_ is not None else (lambda: step(parts=parts))
+            go()
+            k0, k1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            k0.record(stream)
+            for _ in range(a.steps):
+                go()
+            k1.record(stream)
+        barrier()
+        return k0.elapsed_time(k1) / (a.steps * L)
+
+    tile_ms = timed_parts(1)
+    merge_ms = timed_parts(2)
 
     # ---- end to end: host buffers per layer through the host-buffer entry point
     e2e_ms, h2d, d2h = None, 0, 0
@@ -283,6 +294,7 @@ def run_ours(a):
         def step_host():
             for l in range(L):
                 ctx.attention_host(plans[l], hQ[l], hK[l], hV[l], O16=hO[l], stream=stream)
+            ctx.host_flush(stream)
 
         with torch.cuda.stream(stream):
             step_host()
@@ -321,7 +333,8 @@ def run_ours(a):
             "ms_per_step": ms_step, "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "f16",
             "data": "synthetic", "config": workload_config(a, world),
             "roofline": {"bound": "tensor", "achieved": ach_tf, "peak": pk["tf_sustained"], "unit": "TFLOP/s",
-                         "frac": ach_tf / pk["tf_sustained"], "traffic": None,
+                         "frac": ach_tf / pk["tf_sustained"], "traffic": NCU_TRAFFIC_BYTES_PER_UNIT * st.total_units,
+                         "traffic_note": "ncu dram read+write of a 32-sequence launch scaled by units; algorithmic bytes per launch = %d" % bytes_launch,
                          "kernel": "attn_tile_kernel", "ms_per_launch": tile_ms, "peak_source": pk["src"] + " sustained bf16",
                          "hbm_achieved_gbs": ach_gbs, "hbm_peak_gbs": pk["hbm"], "hbm_frac": ach_gbs / pk["hbm"],
                          "slower_bound": "tensor" if t_tensor >= t_hbm else "hbm",

@@ -146,9 +146,16 @@ int llattn_attention(llattn_ctx* ctx, const llattn_plan* plan, const llattn_io* 
  * context's scratch), 2 only the merge of the partials already there, 3 both (= llattn_attention). */
 int llattn_attention_parts(llattn_ctx* ctx, const llattn_plan* plan, const llattn_io* io, int parts, void* stream);
 
-/* Same, with Q/Kf/Vf and the requested outputs in HOST memory (pinned for asynchronous copies): copies in, runs,
- * copies out, on `stream`. The KV cache stays on the device, as in the reference engine. */
+/* Same, with Q/Kf/Vf and the requested outputs in HOST memory (pinned, so the copies are asynchronous). The KV cache
+ * stays on the device, as in the reference engine. Consecutive calls are pipelined: a call's inputs go up on the
+ * context's own copy stream, its kernels run on `stream`, its outputs come down on a second copy stream, so the upload
+ * of one call and the download of the previous one overlap the kernels in between. Host inputs must stay unchanged,
+ * and host outputs are complete, only once llattn_host_flush has been ordered on a stream and that stream has reached
+ * it. Not for use inside stream capture. */
 int llattn_attention_host(llattn_ctx* ctx, const llattn_plan* plan, const llattn_io* io_host, void* stream);
+
+/* Makes `stream` wait for every download llattn_attention_host has issued so far. */
+int llattn_host_flush(llattn_ctx* ctx, void* stream);
 
 /* ---- attention without any allocation, for callers that cannot allocate device memory.
  * No counterpart in the reference. Some hosts of this library may not call cudaMalloc at the point where they need

@@ -26,7 +26,7 @@ EXPORTS = (
     "llattn_version", "llattn_last_error", "llattn_pick_bpc", "llattn_chunks_for", "llattn_kv_commit",
     "llattn_kv_commit_paged", "llattn_attn_partial", "llattn_attn_combine", "llattn_create", "llattn_destroy",
     "llattn_plan_create", "llattn_plan_destroy", "llattn_plan_get_stats", "llattn_plan_preview", "llattn_attention",
-    "llattn_attention_parts", "llattn_attention_host", "llattn_device_status", "llattn_attention_static",
+    "llattn_attention_parts", "llattn_attention_host", "llattn_host_flush", "llattn_device_status", "llattn_attention_static",
 )
 
 
@@ -87,6 +87,7 @@ def lib() -> ctypes.CDLL:
         L.llattn_attention.argtypes = [c_void_p, c_void_p, POINTER(_IO), c_void_p]
         L.llattn_attention_parts.argtypes = [c_void_p, c_void_p, POINTER(_IO), c_int, c_void_p]
         L.llattn_attention_host.argtypes = [c_void_p, c_void_p, POINTER(_IO), c_void_p]
+        L.llattn_host_flush.argtypes = [c_void_p, c_void_p]
         L.llattn_device_status.argtypes = [c_void_p, c_void_p, POINTER(c_int)]
         L.llattn_attention_static.argtypes = [c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_float,
                                               c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p]
@@ -258,6 +259,10 @@ class Context:
         """Q/Kf/Vf and the outputs are HOST tensors (pinned for asynchronous copies)."""
         io = _IO(_ptr(Q), _ptr(Kf), _ptr(Vf), _ptr(O16), _ptr(O32), _ptr(LSE), _ptr(q8), _ptr(s8), _ptr(sum8), scale)
         _check(lib().llattn_attention_host(self._h, plan._h, byref(io), _stream(stream)))
+
+    def host_flush(self, stream=None) -> None:
+        """Orders every download issued by attention_host so far before later work on `stream`."""
+        _check(lib().llattn_host_flush(self._h, _stream(stream)))
 
     def device_status(self, stream=None) -> int:
         code = c_int(0)

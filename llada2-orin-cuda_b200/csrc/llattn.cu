@@ -47,8 +47,12 @@ struct llattn_ctx {
     int* err_word = nullptr;          // device
     void* workspace = nullptr;        // device: partial results (grow-only)
     size_t workspace_bytes = 0;
-    void* stage = nullptr;            // device staging for the host-buffer entry point (grow-only)
-    size_t stage_bytes = 0;
+    void* stage = nullptr;            // device staging for the host-buffer entry point: two slots (grow-only)
+    size_t stage_bytes = 0, stage_slot_bytes = 0;
+    bool host_ready = false;          // copy streams and events of the host-buffer path exist
+    int host_slot = 0;
+    cudaStream_t s_in = nullptr, s_out = nullptr;
+    cudaEvent_t ev_in[2] = {}, ev_comp[2] = {}, ev_out[2] = {};
     std::mutex mu;
 };
 

@@ -173,6 +173,11 @@ void llattn_destroy(llattn_ctx* c) {
     cudaFree(c->err_word);
     cudaFree(c->workspace);
     cudaFree(c->stage);
+    if (c->host_ready) {
+        cudaStreamDestroy(c->s_in);
+        cudaStreamDestroy(c->s_out);
+        for (int i = 0; i < 2; ++i) { cudaEventDestroy(c->ev_in[i]); cudaEventDestroy(c->ev_comp[i]); cudaEventDestroy(c->ev_out[i]); }
+    }
     delete c;
 }
 
@@ -298,21 +303,41 @@ int llattn_attention_parts(llattn_ctx* c, const llattn_plan* pl, const llattn_io
     return LLATTN_OK;
 }
 
+// Host-buffer path, pipelined over consecutive calls: inputs go up on the context's own copy stream into one of two
+// staging slots, the kernels run on the caller's stream once their slot has landed, results go down on a second copy
+// stream. Call k's upload therefore overlaps call k-1's kernels and call k-1's download overlaps call k's kernels.
 int llattn_attention_host(llattn_ctx* c, const llattn_plan* pl, const llattn_io* h, void* stream) {
     using namespace llattn;
     if (!c || !pl || pl->ctx != c) return fail(LLATTN_EINVAL, "attention_host: plan does not belong to this context");
     if (int rc = check_io(h, "attention_host")) return rc;
+    int dev = -1;
+    CU(cudaGetDevice(&dev));
+    if (dev != c->device) return fail(LLATTN_EINVAL, "attention_host: current device %d, context device %d", dev, c->device);
     const size_t nq = size_t(pl->stats.nq_total), rows = nq * BLK;
     const size_t bQ = rows * NQH * D * 2, bKV = rows * NKV * D * 2;
     const size_t bO16 = h->O16 ? bQ : 0, bO32 = h->O32 ? rows * NQH * D * 4 : 0, bLSE = h->LSE ? rows * NQH * 4 : 0;
     const size_t bq8 = h->q8 ? rows * 2048 : 0, bs8 = h->q8 ? rows * NQH * 4 : 0;
     auto up = [](size_t x) { return (x + 255) / 256 * 256; };
     const size_t need = up(bQ) + 2 * up(bKV) + up(bO16) + up(bO32) + up(bLSE) + up(bq8) + 2 * up(bs8);
-    {
-        std::lock_guard<std::mutex> lk(c->mu);
-        if (int rc = grow(&c->stage, &c->stage_bytes, need)) return rc;
+    std::lock_guard<std::mutex> lk(c->mu);
+    if (!c->host_ready) {
+        CU(cudaStreamCreateWithFlags(&c->s_in, cudaStreamNonBlocking));
+        CU(cudaStreamCreateWithFlags(&c->s_out, cudaStreamNonBlocking));
+        for (int i = 0; i < 2; ++i) {
+            CU(cudaEventCreateWithFlags(&c->ev_in[i], cudaEventDisableTiming));
+            CU(cudaEventCreateWithFlags(&c->ev_comp[i], cudaEventDisableTiming));
+            CU(cudaEventCreateWithFlags(&c->ev_out[i], cudaEventDisableTiming));
+        }
+        c->host_ready = true;
     }
-    uint8_t* d = static_cast<uint8_t*>(c->stage);
+    if (2 * need > c->stage_bytes) {          // growing frees the old staging area: nothing may still be using it
+        CU(cudaDeviceSynchronize());
+        if (int rc = grow(&c->stage, &c->stage_bytes, 2 * need)) return rc;
+        c->stage_slot_bytes = c->stage_bytes / 2 / 256 * 256;
+    }
+    const int slot = c->host_slot;
+    c->host_slot ^= 1;
+    uint8_t* d = static_cast<uint8_t*>(c->stage) + size_t(slot) * c->stage_slot_bytes;
     cudaStream_t st = as_stream(stream);
     llattn_io dio{};
     uint8_t* dQ = d; d += up(bQ);
@@ -327,18 +352,36 @@ int llattn_attention_host(llattn_ctx* c, const llattn_plan* pl, const llattn_io*
         dio.s8 = reinterpret_cast<float*>(d); d += up(bs8);
         dio.sum8 = reinterpret_cast<int32_t*>(d); d += up(bs8);
     }
-    CU(cudaMemcpyAsync(dQ, h->Q, bQ, cudaMemcpyHostToDevice, st));
-    CU(cudaMemcpyAsync(dK, h->Kf, bKV, cudaMemcpyHostToDevice, st));
-    CU(cudaMemcpyAsync(dV, h->Vf, bKV, cudaMemcpyHostToDevice, st));
-    if (int rc = llattn_attention(c, pl, &dio, stream)) return rc;
-    if (bO16) CU(cudaMemcpyAsync(h->O16, dio.O16, bO16, cudaMemcpyDeviceToHost, st));
-    if (bO32) CU(cudaMemcpyAsync(h->O32, dio.O32, bO32, cudaMemcpyDeviceToHost, st));
-    if (bLSE) CU(cudaMemcpyAsync(h->LSE, dio.LSE, bLSE, cudaMemcpyDeviceToHost, st));
+    // upload: the slot's previous kernels (two calls ago) must have finished reading it
+    CU(cudaStreamWaitEvent(c->s_in, c->ev_comp[slot], 0));
+    CU(cudaMemcpyAsync(dQ, h->Q, bQ, cudaMemcpyHostToDevice, c->s_in));
+    CU(cudaMemcpyAsync(dK, h->Kf, bKV, cudaMemcpyHostToDevice, c->s_in));
+    CU(cudaMemcpyAsync(dV, h->Vf, bKV, cudaMemcpyHostToDevice, c->s_in));
+    CU(cudaEventRecord(c->ev_in[slot], c->s_in));
+    // kernels: after the upload, and after the slot's previous download has drained its output area
+    CU(cudaStreamWaitEvent(st, c->ev_in[slot], 0));
+    CU(cudaStreamWaitEvent(st, c->ev_out[slot], 0));
+    if (int rc = llattn_attention_parts(c, pl, &dio, 3, stream)) return rc;
+    CU(cudaEventRecord(c->ev_comp[slot], st));
+    // download
+    CU(cudaStreamWaitEvent(c->s_out, c->ev_comp[slot], 0));
+    if (bO16) CU(cudaMemcpyAsync(h->O16, dio.O16, bO16, cudaMemcpyDeviceToHost, c->s_out));
+    if (bO32) CU(cudaMemcpyAsync(h->O32, dio.O32, bO32, cudaMemcpyDeviceToHost, c->s_out));
+    if (bLSE) CU(cudaMemcpyAsync(h->LSE, dio.LSE, bLSE, cudaMemcpyDeviceToHost, c->s_out));
     if (bq8) {
-        CU(cudaMemcpyAsync(h->q8, dio.q8, bq8, cudaMemcpyDeviceToHost, st));
-        CU(cudaMemcpyAsync(h->s8, dio.s8, bs8, cudaMemcpyDeviceToHost, st));
-        CU(cudaMemcpyAsync(h->sum8, dio.sum8, bs8, cudaMemcpyDeviceToHost, st));
+        CU(cudaMemcpyAsync(h->q8, dio.q8, bq8, cudaMemcpyDeviceToHost, c->s_out));
+        CU(cudaMemcpyAsync(h->s8, dio.s8, bs8, cudaMemcpyDeviceToHost, c->s_out));
+        CU(cudaMemcpyAsync(h->sum8, dio.sum8, bs8, cudaMemcpyDeviceToHost, c->s_out));
     }
+    CU(cudaEventRecord(c->ev_out[slot], c->s_out));
+    return LLATTN_OK;
+}
+
+int llattn_host_flush(llattn_ctx* c, void* stream) {
+    if (!c) return fail(LLATTN_EINVAL, "host_flush: null context");
+    std::lock_guard<std::mutex> lk(c->mu);
+    if (!c->host_ready) return LLATTN_OK;
+    for (int i = 0; i < 2; ++i) CU(cudaStreamWaitEvent(as_stream(stream), c->ev_out[i], 0));
     return LLATTN_OK;
 }
 

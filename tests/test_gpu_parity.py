@@ -99,6 +99,7 @@ def run_batched(api, ctx, cases, want=("O32", "LSE"), nctas=0, host=False):
     if host:
         tq, tk, tv = (torch.from_numpy(x).pin_memory() for x in (Q, Kf, Vf))
         ctx.attention_host(plan, tq, tk, tv, **out)
+        ctx.host_flush()
     else:
         ctx.attention(plan, dev(Q), dev(Kf), dev(Vf), **out)
     assert ctx.device_status() == 0
