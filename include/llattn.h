@@ -51,6 +51,10 @@ const char* llattn_last_error(void);
 int llattn_pick_bpc(int nblocks, int nbatch);
 int llattn_chunks_for(int nblocks, int blocks_per_chunk);
 
+/* 32-token blocks per MMA tile of this build (3 or 4). Runs of blocks that start on a multiple of it keep tiles full;
+ * any split is correct. No counterpart in the reference. */
+int llattn_tile_units(void);
+
 /* ---- block commit.
  * Stands in for attn::kv_commit<<<dim3(4, nb), 128, 0, st>>>(Kf, Vf, cache, max_blocks, blk)
  * (engine/attn.cu:369; call sites engine/engine.cu:591 and :656): block j of Kf/Vf becomes record blk + j of every

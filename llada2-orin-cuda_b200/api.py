@@ -23,7 +23,7 @@ SCALE = 0.08838834764831845  # 1/sqrt(128), the constant engine/engine.cu:430 pa
 OK, EINVAL, ECUDA, ENOMEM, EDEVICE = 0, 1, 2, 3, 4
 
 EXPORTS = (
-    "llattn_version", "llattn_last_error", "llattn_pick_bpc", "llattn_chunks_for", "llattn_kv_commit",
+    "llattn_version", "llattn_last_error", "llattn_pick_bpc", "llattn_chunks_for", "llattn_tile_units", "llattn_kv_commit",
     "llattn_kv_commit_paged", "llattn_attn_partial", "llattn_attn_combine", "llattn_create", "llattn_destroy",
     "llattn_plan_create", "llattn_plan_destroy", "llattn_plan_get_stats", "llattn_plan_preview", "llattn_attention",
     "llattn_attention_parts", "llattn_attention_host", "llattn_host_flush", "llattn_device_status", "llattn_attention_static",
@@ -121,6 +121,11 @@ def _stream(stream) -> Optional[int]:
 def pick_bpc(nblocks: int, nbatch: int) -> int:
     """attn::pick_bpc (engine/attn.cu:361-364)."""
     return lib().llattn_pick_bpc(nblocks, nbatch)
+
+
+def tile_units() -> int:
+    """32-token blocks per MMA tile of the loaded build."""
+    return lib().llattn_tile_units()
 
 
 def chunks_for(nblocks: int, bpc: int) -> int:

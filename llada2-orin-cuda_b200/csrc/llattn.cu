@@ -116,6 +116,7 @@ int llattn_pick_bpc(int nblocks, int nbatch) {
     return std::max(1, (nblocks + want - 1) / want);
 }
 int llattn_chunks_for(int nblocks, int bpc) { return nblocks <= 0 ? 1 : (nblocks + bpc - 1) / bpc; }
+int llattn_tile_units(void) { return llattn::TILE_UNITS; }
 
 // ------------------------------------------------------------------------------------------------------ commit
 

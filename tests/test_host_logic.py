@@ -70,7 +70,7 @@ def test_planner_covers_every_unit_once(api, lengths, nq, nctas):
         key = (seq, qb, kvh)
         cover = seen.setdefault(key, [0, 0])
         assert rec0 == cover[0], "runs of a tile must be consecutive"
-        assert rec0 % 4 == 0, "cuts fall on 128-key tile boundaries"
+        assert rec0 % api.tile_units() == 0, "cuts fall on MMA tile boundaries"
         assert nrec + fresh > 0
         cover[0] += nrec
         cover[1] += fresh
