@@ -359,6 +359,18 @@ def run_ours(a):
 
 
 if __name__ == "__main__":
+    # Libraries (NCCL's version banner, torchrun notices) may write to stdout; the contract is ONE JSON line there. Everything
+    # written to fd 1 from here on goes to stderr, and the JSON line is written to the saved stdout.
+    _real_stdout = os.fdopen(os.dup(1), "w")
+    sys.stdout.flush()
+    os.dup2(2, 1)
+    _print = print
+
+    def print(*a, **k):  # noqa: A001  (only the JSON lines use print in this file)
+        k.pop("flush", None)
+        _print(*a, file=_real_stdout, **k)
+        _real_stdout.flush()
+
     args = parse()
     if args.impl == "reference":
         run_reference(args)
