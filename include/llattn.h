@@ -65,6 +65,14 @@ int llattn_kv_commit(const void* Kf, const void* Vf, void* cache, int max_blocks
  * (`pages` is a device array of nb * 4 indices). No counterpart in the reference, whose cache is contiguous. */
 int llattn_kv_commit_paged(const void* Kf, const void* Vf, void* pool, const int32_t* pages, int nb, void* stream);
 
+/* ---- producer of the attention inputs.
+ * Stands in for ops::qk_norm_rope<<<dim3(T, 3), 256, 0, st>>>(qkv, pos, gq, gk, eps, inv_freq, q, k, v)
+ * (engine/ops.cu:429-453; call sites engine/engine.cu:427 and :589): per-head RMSNorm of q and k with weights gq/gk
+ * [128], RoPE on the first 64 dims at position pos[t] with inv_freq [32] and bf16-rounded cos/sin, v converted;
+ * qkv [T][3072] fp32 in; q [T][16][128], k and v [T][4][128] fp16 out. Same arithmetic, same order: bit-identical. */
+int llattn_qk_norm_rope(const float* qkv, const int32_t* pos, const float* gq, const float* gk, float eps,
+                        const float* inv_freq, void* q, void* k, void* v, int T, void* stream);
+
 /* ---- the reference operator pair on caller-owned buffers.
  * llattn_args mirrors attn::Args (engine/attn.cu:51-64) field for field. */
 typedef struct llattn_args {

@@ -24,7 +24,7 @@ OK, EINVAL, ECUDA, ENOMEM, EDEVICE = 0, 1, 2, 3, 4
 
 EXPORTS = (
     "llattn_version", "llattn_last_error", "llattn_pick_bpc", "llattn_chunks_for", "llattn_tile_units", "llattn_kv_commit",
-    "llattn_kv_commit_paged", "llattn_attn_partial", "llattn_attn_combine", "llattn_create", "llattn_destroy",
+    "llattn_kv_commit_paged", "llattn_qk_norm_rope", "llattn_attn_partial", "llattn_attn_combine", "llattn_create", "llattn_destroy",
     "llattn_plan_create", "llattn_plan_destroy", "llattn_plan_get_stats", "llattn_plan_preview", "llattn_attention",
     "llattn_attention_parts", "llattn_attention_host", "llattn_host_flush", "llattn_device_status", "llattn_attention_static",
 )
@@ -73,6 +73,8 @@ def lib() -> ctypes.CDLL:
         L.llattn_chunks_for.argtypes = [c_int, c_int]
         L.llattn_kv_commit.argtypes = [c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_void_p]
         L.llattn_kv_commit_paged.argtypes = [c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_void_p]
+        L.llattn_qk_norm_rope.argtypes = [c_void_p, c_void_p, c_void_p, c_void_p, c_float, c_void_p, c_void_p, c_void_p,
+                                          c_void_p, c_int, c_void_p]
         L.llattn_attn_partial.argtypes = [POINTER(_Args), c_int, c_void_p, c_void_p]
         L.llattn_attn_combine.argtypes = [c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_void_p, c_void_p,
                                           c_void_p, c_void_p, c_int, c_void_p]
@@ -148,6 +150,22 @@ def kv_commit_paged(Kf, Vf, pool, pages, stream=None) -> None:
     if pages.numel() != nb * NKV:
         raise ValueError("pages must hold nb * 4 indices")
     _check(lib().llattn_kv_commit_paged(_ptr(Kf), _ptr(Vf), _ptr(pool), _ptr(pages), nb, _stream(stream)))
+
+
+# ------------------------------------------------------------------ producer
+
+def inv_freq(theta: float = 3e6):
+    """The 32 RoPE frequencies the engine uploads (engine/engine.cu:275-277): theta^(-2i/64) as float32."""
+    import numpy as np
+    return np.array([np.float32(1.0 / (float(theta) ** (2.0 * i / 64.0))) for i in range(32)], np.float32)
+
+
+def qk_norm_rope(qkv, pos, gq, gk, eps, inv_freq_t, q, k, v, stream=None) -> None:
+    """ops::qk_norm_rope<<<dim3(T, 3), 256>>>(qkv, pos, gq, gk, eps, inv_freq, q, k, v) (engine/ops.cu:429).
+    qkv fp32 [T][3072], pos int32 [T], gq/gk fp32 [128], inv_freq fp32 [32]; q fp16 [T][16][128], k/v fp16 [T][4][128]."""
+    T = qkv.shape[0]
+    _check(lib().llattn_qk_norm_rope(_ptr(qkv), _ptr(pos), _ptr(gq), _ptr(gk), eps, _ptr(inv_freq_t), _ptr(q), _ptr(k),
+                                     _ptr(v), T, _stream(stream)))
 
 
 # ------------------------------------------------------------------ the reference operator pair

@@ -15,6 +15,7 @@
 #include "kv_commit.cuh"
 #include "attn_kernel.cuh"
 #include "merge_kernel.cuh"
+#include "qk_norm_rope.cuh"
 
 namespace {
 
@@ -140,6 +141,19 @@ int llattn_kv_commit_paged(const void* Kf, const void* Vf, void* pool, const int
     if (nb == 0) return LLATTN_OK;
     llattn::kv_commit_kernel<<<dim3(llattn::NKV, nb), llattn::COMMIT_THREADS, 0, as_stream(stream)>>>(
         static_cast<const half*>(Kf), static_cast<const half*>(Vf), static_cast<uint8_t*>(pool), pages, 0, 0);
+    CU(cudaGetLastError());
+    return LLATTN_OK;
+}
+
+// ------------------------------------------------------------------------------------------------------ producer
+
+int llattn_qk_norm_rope(const float* qkv, const int32_t* pos, const float* gq, const float* gk, float eps,
+                        const float* inv_freq, void* q, void* k, void* v, int T, void* stream) {
+    if (!qkv || !pos || !gq || !gk || !inv_freq || !q || !k || !v) return fail(LLATTN_EINVAL, "qk_norm_rope: null pointer");
+    if (T < 0 || T > 1 << 24) return fail(LLATTN_EINVAL, "qk_norm_rope: T = %d", T);
+    if (T == 0) return LLATTN_OK;
+    llattn::qk_norm_rope_kernel<<<dim3(T, 3), llattn::ROPE_THREADS, 0, as_stream(stream)>>>(
+        qkv, pos, gq, gk, eps, inv_freq, static_cast<half*>(q), static_cast<half*>(k), static_cast<half*>(v));
     CU(cudaGetLastError());
     return LLATTN_OK;
 }

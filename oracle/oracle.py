@@ -54,6 +54,7 @@ def lib() -> ctypes.CDLL:
         L.orc_h2f.argtypes = [ctypes.c_uint16]
         L.orc_h2f.restype = ctypes.c_float
         L.orc_num_threads.restype = i32
+        L.orc_qk_norm_rope.argtypes = [vp, vp, vp, vp, ctypes.c_float, vp, vp, vp, vp, i32]
     return _lib
 
 
@@ -112,6 +113,20 @@ def fake_quant_c(x: np.ndarray, group: int) -> np.ndarray:
     y = np.empty_like(x)
     lib().orc_fake_quant(_p(x), _p(y), x.size // group, group)
     return y
+
+
+def qk_norm_rope(qkv, pos, gq, gk, eps, inv_freq):
+    """Producer of the attention inputs (engine/ops.cu:429-453) in double precision with the kernel's bf16 / fp16
+    roundings. qkv float32 [T][3072], pos int32 [T], gq/gk float32 [128], inv_freq float32 [32].
+    Returns q float16 [T][16][128], k, v float16 [T][4][128]."""
+    T = qkv.shape[0]
+    q = np.empty((T, NQH, D), np.float16)
+    k = np.empty((T, NKV, D), np.float16)
+    v = np.empty((T, NKV, D), np.float16)
+    lib().orc_qk_norm_rope(_p(np.ascontiguousarray(qkv, np.float32)), _p(np.ascontiguousarray(pos, np.int32)),
+                           _p(np.ascontiguousarray(gq, np.float32)), _p(np.ascontiguousarray(gk, np.float32)), float(eps),
+                           _p(np.ascontiguousarray(inv_freq, np.float32)), _p(q), _p(k), _p(v), T)
+    return q, k, v
 
 
 def frag_pos(c: int) -> int:

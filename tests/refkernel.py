@@ -58,3 +58,24 @@ def attention(Q, Kf, Vf, cache, max_blocks, nblocks, bpc=0, int8=False):
     assert rc == 0, rc
     torch.cuda.synchronize()
     return (q8, s8, sum8) if int8 else O
+
+
+OPS_PATH = os.path.join(ROOT, "oracle", "_ref", "libops_ref.so")
+_ops = None
+
+
+def ops_available() -> bool:
+    return os.path.exists(OPS_PATH)
+
+
+def qk_norm_rope(qkv, pos, gq, gk, eps, inv_freq, q, k, v):
+    """The reference's own ops::qk_norm_rope (engine/ops.cu:429) on device tensors."""
+    import torch
+    global _ops
+    if _ops is None:
+        _ops = ctypes.CDLL(OPS_PATH)
+        vp = ctypes.c_void_p
+        _ops.ref_qk_norm_rope.argtypes = [vp, vp, vp, vp, ctypes.c_float, vp, vp, vp, vp, ctypes.c_int, vp]
+    rc = _ops.ref_qk_norm_rope(qkv.data_ptr(), pos.data_ptr(), gq.data_ptr(), gk.data_ptr(), eps, inv_freq.data_ptr(),
+                               q.data_ptr(), k.data_ptr(), v.data_ptr(), qkv.shape[0], torch.cuda.current_stream().cuda_stream)
+    assert rc == 0, rc
