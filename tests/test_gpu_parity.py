@@ -276,3 +276,53 @@ def test_host_buffer_entry_point(api, ctx, orc, pkg):
     torch.cuda.synchronize()
     for k in ("O32", "O16", "LSE"):
         assert np.array_equal(a[k], b[k])
+
+
+def test_twenty_layer_step_inside_a_cuda_graph(api, ctx, orc, pkg):
+    """BASELINE config 2 in shape: batch 1, 20 layers with their own caches, the whole step captured once as a CUDA
+    graph and replayed (the reference replays a captured step too, engine/decode.cu:318-341). Replays must reproduce
+    the eager results bit for bit, and stay correct after the inputs change in place."""
+    L, n = 20, 24
+    wl = pkg.workload
+    caches, plans, Qs, Ks, Vs, want = [], [], [], [], [], []
+    for l in range(L):
+        Kc, Vc = wl.context_blocks(n, seq=500, layer=l)
+        Q, Kf, Vf = wl.query_blocks(1, seq=500, layer=l)
+        cache = np.zeros((4, n + 1, orc.REC_BYTES), np.uint8)
+        orc.kv_commit(Kc, Vc, cache, n + 1, 0)
+        caches.append(dev(cache)); Qs.append(Q); Ks.append(Kf); Vs.append(Vf)
+        plans.append(ctx.plan([api.Seq(cache=caches[-1], nblocks=n)]))
+        want.append(orc.attention(Q, Kf, Vf, cache, n + 1, n, dq_mode=1)[0])
+    dQ, dK, dV = dev(np.stack(Qs)), dev(np.stack(Ks)), dev(np.stack(Vs))
+    O = torch.zeros((L, 32, 16, 128), dtype=torch.float32, device="cuda")
+    stream = torch.cuda.Stream()
+
+    def step():
+        for l in range(L):
+            ctx.attention(plans[l], dQ[l], dK[l], dV[l], O32=O[l], stream=stream)
+
+    with torch.cuda.stream(stream):
+        step()
+        stream.synchronize()
+        eager = O.clone()
+        g = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(g, stream=stream):
+            step()
+        O.zero_()
+        g.replay()
+        stream.synchronize()
+    assert ctx.device_status(stream) == 0
+    assert torch.equal(O, eager)
+    got = O.cpu().numpy()
+    for l in range(L):
+        assert rel_l2(got[l], want[l]) <= TOL_L2 and relmax(got[l], want[l]) <= TOL_O
+    # new inputs in the same buffers: the replayed graph reads them
+    with torch.cuda.stream(stream):
+        dQ.copy_(dev(np.stack(Qs[::-1])))
+        g.replay()
+        stream.synchronize()
+    Q_last = Qs[L - 1]
+    w0 = orc.attention(Q_last, Ks[0], Vs[0], caches[0].cpu().numpy(), n + 1, n, dq_mode=1)[0]
+    assert rel_l2(O[0].cpu().numpy(), w0) <= TOL_L2
+    for p_ in plans:
+        p_.close()
