@@ -189,6 +189,27 @@ int llattn_attention_static(const void* Q, const void* Kf, const void* Vf, const
                             int nb, float scale, void* O16, float* O32, float* LSE, int8_t* q8, float* s8, int32_t* sum8,
                             int* err_word, void* stream);
 
+/* ---- page manager with prefix reuse for the record pools of the batched path (host only, no CUDA call).
+ * Generalises the reference's single-sequence prefix cache (engine/decode.cu:469-481: committed blocks whose token ids
+ * equal the new prompt's leading full blocks are kept) to many sequences over one pool. A page is one committed
+ * 32-token block; its record for kv head h of any layer is record `page * 4 + h` of that layer's pool. Sequences that
+ * share a prefix of token blocks share its pages; pages of closed sequences stay reusable until their slot is needed
+ * (least recently used first). The caller owns the pools and commits the pages reported as not reused. */
+typedef struct llattn_kvpool llattn_kvpool;
+int llattn_kvpool_create(int npages, llattn_kvpool** out);
+void llattn_kvpool_destroy(llattn_kvpool* pool);
+/* Opens a sequence on a prompt: its ntokens / 32 full blocks get pages (pages_out, in block order, may be NULL);
+ * *reused_blocks leading blocks were found committed already and need no prefill. */
+int llattn_kvpool_open(llattn_kvpool* pool, const int32_t* tokens, int ntokens, int32_t* seq_id, int32_t* reused_blocks,
+                       int32_t* pages_out, int pages_cap);
+/* A decoded block of 32 final token ids becomes the sequence's next page (*reused = 1 if an identical continuation
+ * was already committed by another sequence). */
+int llattn_kvpool_append(llattn_kvpool* pool, int32_t seq_id, const int32_t* block_tokens, int32_t* page_out, int32_t* reused);
+int llattn_kvpool_pages(llattn_kvpool* pool, int32_t seq_id, int32_t* pages_out, int cap, int32_t* nblocks);
+int llattn_kvpool_close(llattn_kvpool* pool, int32_t seq_id);
+/* out6 = pages, free, cached (reusable, unreferenced), block hits, block misses, evictions */
+int llattn_kvpool_stats(llattn_kvpool* pool, int64_t* out6);
+
 /* Reads (and clears) the context's device error word; synchronises `stream`. 0 = no kernel wait ran out. */
 int llattn_device_status(llattn_ctx* ctx, void* stream, int* code);
 

@@ -26,7 +26,9 @@ EXPORTS = (
     "llattn_version", "llattn_last_error", "llattn_pick_bpc", "llattn_chunks_for", "llattn_tile_units", "llattn_kv_commit",
     "llattn_kv_commit_paged", "llattn_qk_norm_rope", "llattn_attn_partial", "llattn_attn_combine", "llattn_create", "llattn_destroy",
     "llattn_plan_create", "llattn_plan_destroy", "llattn_plan_get_stats", "llattn_plan_preview", "llattn_attention",
-    "llattn_attention_parts", "llattn_attention_host", "llattn_host_flush", "llattn_device_status", "llattn_attention_static",
+    "llattn_attention_parts", "llattn_attention_host", "llattn_host_flush", "llattn_device_status",
+    "llattn_kvpool_create", "llattn_kvpool_destroy", "llattn_kvpool_open", "llattn_kvpool_append", "llattn_kvpool_pages",
+    "llattn_kvpool_close", "llattn_kvpool_stats", "llattn_attention_static",
 )
 
 
@@ -90,6 +92,14 @@ def lib() -> ctypes.CDLL:
         L.llattn_attention_parts.argtypes = [c_void_p, c_void_p, POINTER(_IO), c_int, c_void_p]
         L.llattn_attention_host.argtypes = [c_void_p, c_void_p, POINTER(_IO), c_void_p]
         L.llattn_host_flush.argtypes = [c_void_p, c_void_p]
+        L.llattn_kvpool_create.argtypes = [c_int, POINTER(c_void_p)]
+        L.llattn_kvpool_destroy.argtypes = [c_void_p]
+        L.llattn_kvpool_destroy.restype = None
+        L.llattn_kvpool_open.argtypes = [c_void_p, c_void_p, c_int, POINTER(c_int32), POINTER(c_int32), c_void_p, c_int]
+        L.llattn_kvpool_append.argtypes = [c_void_p, c_int32, c_void_p, POINTER(c_int32), POINTER(c_int32)]
+        L.llattn_kvpool_pages.argtypes = [c_void_p, c_int32, c_void_p, c_int, POINTER(c_int32)]
+        L.llattn_kvpool_close.argtypes = [c_void_p, c_int32]
+        L.llattn_kvpool_stats.argtypes = [c_void_p, c_void_p]
         L.llattn_device_status.argtypes = [c_void_p, c_void_p, POINTER(c_int)]
         L.llattn_attention_static.argtypes = [c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_float,
                                               c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p]
@@ -314,3 +324,70 @@ class Plan:
             self.close()
         except Exception:
             pass
+
+
+class KvPool:
+    """Host-side page manager with prefix reuse (llattn_kvpool_*): pages are committed 32-token blocks, shared by
+    sequences with a common prefix of token blocks, recycled least-recently-used once no open sequence holds them.
+    Record of (page p, kv head h) in any layer's pool: p * 4 + h."""
+
+    def __init__(self, npages: int):
+        self._h = c_void_p()
+        _check(lib().llattn_kvpool_create(npages, byref(self._h)))
+
+    def close_pool(self) -> None:
+        if self._h:
+            lib().llattn_kvpool_destroy(self._h)
+            self._h = c_void_p()
+
+    def __del__(self):
+        try:
+            self.close_pool()
+        except Exception:
+            pass
+
+    def open(self, tokens):
+        """-> (seq_id, reused_blocks, pages of the prompt's full blocks)."""
+        import numpy as np
+        tok = np.ascontiguousarray(tokens, np.int32)
+        full = len(tok) // 32
+        pages = np.zeros(max(full, 1), np.int32)
+        sid, reused = c_int32(0), c_int32(0)
+        _check(lib().llattn_kvpool_open(self._h, tok.ctypes.data, len(tok), byref(sid), byref(reused), pages.ctypes.data, full))
+        return sid.value, reused.value, pages[:full].copy()
+
+    def append(self, seq_id: int, block_tokens):
+        import numpy as np
+        tok = np.ascontiguousarray(block_tokens, np.int32)
+        if tok.size != 32:
+            raise ValueError("a block is 32 token ids")
+        page, reused = c_int32(0), c_int32(0)
+        _check(lib().llattn_kvpool_append(self._h, seq_id, tok.ctypes.data, byref(page), byref(reused)))
+        return page.value, bool(reused.value)
+
+    def pages(self, seq_id: int):
+        import numpy as np
+        n = c_int32(0)
+        _check(lib().llattn_kvpool_pages(self._h, seq_id, None, 0, byref(n)))
+        out = np.zeros(max(n.value, 1), np.int32)
+        _check(lib().llattn_kvpool_pages(self._h, seq_id, out.ctypes.data, n.value, byref(n)))
+        return out[:n.value].copy()
+
+    def close(self, seq_id: int) -> None:
+        _check(lib().llattn_kvpool_close(self._h, seq_id))
+
+    def stats(self) -> dict:
+        import numpy as np
+        o = np.zeros(6, np.int64)
+        _check(lib().llattn_kvpool_stats(self._h, o.ctypes.data))
+        return dict(zip(("pages", "free", "cached", "hits", "misses", "evictions"), (int(x) for x in o)))
+
+    @staticmethod
+    def page_table(pages, head_stride=None):
+        """int32 [4][head_stride] record indices (page * 4 + head) for llattn_seq.pages / Seq(pages=...)."""
+        import numpy as np
+        pages = np.asarray(pages, np.int32)
+        hs = len(pages) if head_stride is None else head_stride
+        t = np.zeros((NKV, hs), np.int32)
+        t[:, :len(pages)] = pages[None, :] * NKV + np.arange(NKV, dtype=np.int32)[:, None]
+        return t

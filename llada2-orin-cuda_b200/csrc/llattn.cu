@@ -161,6 +161,7 @@ int llattn_qk_norm_rope(const float* qkv, const int32_t* pos, const float* gq, c
 }  // extern "C"
 
 #include "llattn_attention.inl"
+#include "kvpool.inl"
 
 // ====================================================================================================== no-allocation entry point
 // Scratch for llattn_attention_static: partial results (un-normalised O, reference maximum, row sum) of up to

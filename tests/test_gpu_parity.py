@@ -254,6 +254,55 @@ def test_paged_cache(api, ctx, orc, pkg):
     assert relmax(O.cpu().numpy(), O1) <= TOL_O
 
 
+def test_page_manager_prefix_reuse_end_to_end(api, ctx, orc, pkg):
+    """Two requests that share a 5-block prompt prefix, served from one record pool through the page manager: the
+    second commits only its own blocks, and both attend over page tables; results equal the contiguous-cache oracle."""
+    wl = pkg.workload
+    g = np.random.default_rng(11)
+    ids_a = g.integers(0, 150000, 32 * 8, dtype=np.int32)
+    ids_b = np.concatenate([ids_a[:32 * 5], g.integers(0, 150000, 32 * 4, dtype=np.int32)])
+    Ka, Va = wl.context_blocks(8, seq=60)
+    Kb, Vb = wl.context_blocks(9, seq=61)
+    Kb[:5], Vb[:5] = Ka[:5], Va[:5]                       # same tokens after the same prefix: same K/V
+    mgr = api.KvPool(40)
+    pool = torch.zeros((40 * 4, orc.REC_BYTES), dtype=torch.uint8, device="cuda")
+    sa, ra, pa = mgr.open(ids_a)
+    assert ra == 0
+    api.kv_commit_paged(dev(Ka), dev(Va), pool, dev(api.KvPool.page_table(pa).T.copy()))
+    torch.cuda.synchronize()
+    snap = pool.cpu().numpy().copy()
+    sb, rb, pb = mgr.open(ids_b)
+    assert rb == 5 and pb[:5].tolist() == pa[:5].tolist()
+    api.kv_commit_paged(dev(Kb[rb:]), dev(Vb[rb:]), pool, dev(api.KvPool.page_table(pb[rb:]).T.copy()))
+    torch.cuda.synchronize()
+    now = pool.cpu().numpy()
+    shared = (pa[:, None] * 4 + np.arange(4)[None, :]).reshape(-1)
+    assert np.array_equal(now[shared], snap[shared])      # request a's pages were not written again
+    cases = []
+    for (K, V, n, seq) in ((Ka, Va, 8, 60), (Kb, Vb, 9, 61)):
+        Q, Kf, Vf = wl.query_blocks(1, seq=seq)
+        cache = np.zeros((4, n + 1, orc.REC_BYTES), np.uint8)
+        orc.kv_commit(K, V, cache, n + 1, 0)
+        cases.append((Q, Kf, Vf, cache, n + 1, n))
+    ta, tb = dev(api.KvPool.page_table(pa)), dev(api.KvPool.page_table(pb))
+    plan = ctx.plan([api.Seq(cache=pool, pages=ta, nblocks=8, nq=1, q_first=0),
+                     api.Seq(cache=pool, pages=tb, nblocks=9, nq=1, q_first=1)])
+    O = torch.zeros((64, 16, 128), dtype=torch.float32, device="cuda")
+    cat = lambda i: dev(np.concatenate([c[i] for c in cases]))
+    ctx.attention(plan, cat(0), cat(1), cat(2), O32=O)
+    assert ctx.device_status() == 0
+    O = O.cpu().numpy()
+    for i, (Q, Kf, Vf, cache, maxb, n) in enumerate(cases):
+        O1, _ = orc.attention(Q, Kf, Vf, cache, maxb, n, dq_mode=1)
+        assert relmax(O[32 * i:32 * (i + 1)], O1) <= TOL_O
+    # decode commits a block: the manager hands out the next page, the commit fills it
+    blk = g.integers(0, 150000, 32, dtype=np.int32)
+    page, hit = mgr.append(sa, blk)
+    assert not hit and page not in set(pa.tolist()) | set(pb.tolist())
+    mgr.close(sa); mgr.close(sb)
+    assert mgr.stats()["cached"] == 8 + 4 + 1
+
+
 def test_int8_activation_output(api, ctx, orc, pkg):
     n = 12
     Q, Kf, Vf, cache, maxb = make_case(pkg.workload, orc, n, seq=90)
