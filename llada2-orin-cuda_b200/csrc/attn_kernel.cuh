@@ -18,13 +18,16 @@
 // The run's un-normalised O (fp32), reference maximum (log2 units) and row sum go to a partial slot in the format of
 // the reference's Opart/Mpart/Lpart (engine/attn.cu:291-305); merge_kernel.cuh folds the slots of a tile together.
 //
-// Operand layout in shared memory (no swizzle): an operand tile is 16 "chunk rows" of CS bytes; chunk row j holds, for
-// each of up to 128 rows (query rows or keys), the 16 bytes of channels 8j..8j+7 at row*16. Within each group of 8
-// channels the order is (0,4,1,5,2,6,3,7): that is what the shift-free nibble unpack produces, Q and the fresh K are
-// stored in the same order (a dot product does not care) and V's order is undone when O is written out.
-// CS = 128*16: a core matrix (8 rows x 16 bytes) is then 128-byte aligned, which the tensor core needs to fetch it in
-// one shared-memory wavefront (a padded stride halves the MMA rate). Threads therefore store so that the 8 lanes of a
-// quarter warp cover 8 different rows: their 16-byte stores land in distinct banks without padding.
+// Operands. Q (the A operand of S = Q K^T) lives in tensor memory for the whole item: row i in lane i, 64 columns of
+// fp16 pairs. K and V tiles live in shared memory in the 128-byte-swizzle layout: a tile is made of blocks of
+// 128 keys x 128 bytes (64 channels of one key per row; K has two blocks, V a third one whose first column is all
+// ones), and the 16-byte chunk c of key k sits at chunk position c ^ (k % 8). K is read K-major (S), V MN-major (PV).
+// Shared-memory bandwidth is what bounds this kernel (tensor-core operand reads plus the dequantisation's loads and
+// stores), so the layout is chosen to make every access of the dequantisation conflict-free: a warp loads the packed
+// codes of two whole keys (128 contiguous bytes) and each quarter warp stores the eight 16-byte chunks of one key's
+// row. Within each group of 8 channels the order is (0,4,1,5,2,6,3,7): that is what the shift-free nibble unpack
+// produces, Q and the fresh K are stored in the same order (a dot product does not care) and V's order is undone when
+// O is written out.
 //
 // Every wait is bounded (ptx::mbar_wait); a wait that runs out sets a bit in the error word and every role leaves.
 #pragma once
@@ -48,19 +51,18 @@ constexpr int LLATTN_TRACE_EVENTS = 2048;
 #define LLATTN_TR(ev, tile) do {} while (0)
 #endif
 #ifndef LLATTN_SKIP
-#define LLATTN_SKIP 0      // tuning builds only: 1 = no dequant arithmetic, 2 = no softmax arithmetic (results are garbage)
+#define LLATTN_SKIP 0      // tuning builds only: bit 0 = no dequantisation, bit 1 = no softmax arithmetic (results are garbage)
 #endif
 
 constexpr int TILE_UNITS = 4;
-constexpr int CS = 128 * 16;                       // chunk-row stride, bytes: every 8-row core matrix is 128-byte aligned
-constexpr int TILE_BYTES = 16 * CS;                // 32768: Q or K tile
-constexpr int V_ROWS = 18;                         // 16 chunk rows of dims + one holding the ones column + one of zeros
-constexpr int VTILE_BYTES = V_ROWS * CS;           // 36864
+constexpr int KBLOCK = 128 * 128;                  // 16384: 128 keys x 64 channels of fp16, one swizzled block
+constexpr int TILE_BYTES = 2 * KBLOCK;             // K tile: channels 0-63, 64-127
+constexpr int VTILE_BYTES = 3 * KBLOCK;            // V tile: dims 0-63, 64-127, then the block with the ones column
+constexpr int UNIT_BYTES = 32 * 128;               // a unit's 32 keys inside a block
 constexpr int PV_N = 144;                          // dims 0..127, column 128 = row sum, 129..143 unused
 constexpr int NRAW = 8;                            // records in flight (two tiles' worth)
 constexpr int RAW_STRIDE = 4864;                   // 4736 rounded up to a multiple of 128
-constexpr int SM_Q = 0;
-constexpr int SM_K = SM_Q + TILE_BYTES;            // two K tiles
+constexpr int SM_K = 0;                            // two K tiles (every tile base is 1024-byte aligned)
 constexpr int SM_V = SM_K + 2 * TILE_BYTES;        // two V tiles
 constexpr int SM_RAW = SM_V + 2 * VTILE_BYTES;
 constexpr int SM_BAR = SM_RAW + NRAW * RAW_STRIDE;
@@ -73,10 +75,11 @@ constexpr int ATTN_SMEM_BYTES = SM_MISC + 16;
 #define LLATTN_DEQUANT_WARPS 16
 #endif
 constexpr int SOFTMAX_WARPS = 8, DEQUANT_WARPS = LLATTN_DEQUANT_WARPS, DEQUANT_GROUPS = DEQUANT_WARPS / 4;
-constexpr int WARP_PRODUCER = SOFTMAX_WARPS + DEQUANT_WARPS, WARP_MMA = WARP_PRODUCER + 1, WARP_MMA_PV = WARP_MMA + 1;
-constexpr int ATTN_THREADS = 32 * (WARP_MMA_PV + 1);  // 864
+constexpr int WARP_SERVICE = SOFTMAX_WARPS + DEQUANT_WARPS;
+constexpr int WARP_PRODUCER = WARP_SERVICE, WARP_MMA = WARP_SERVICE + 1, WARP_MMA_PV = WARP_SERVICE + 2;
+constexpr int ATTN_THREADS = 32 * (WARP_SERVICE + 3);  // 864
 constexpr int TMEM_COLS = 512;
-constexpr int TM_S = 0, TM_O = 256, TM_L = TM_O + 128;   // S buffers at columns 0 and 128, O at 256..383, row sum at 384
+constexpr int TM_S = 0, TM_O = 256, TM_L = TM_O + 128, TM_Q = 400;   // S at columns 0 and 128, O at 256..383, row sum at 384, Q at 400..463
 constexpr float RESCALE_SLACK = 8.f;
 
 // barrier indices
@@ -124,6 +127,11 @@ __device__ __forceinline__ bool fetch_item(const KParams& p, int idx, WorkItem& 
     return true;
 }
 
+// The same value in every lane, in a form the compiler can see is warp-uniform (a warp reduction): the MMA-issuing warps
+// run warp-uniform code whose operands then stay in uniform registers instead of being moved there before every MMA.
+__device__ __forceinline__ uint32_t uniform_u32(uint32_t x) { return __reduce_max_sync(0xffffffffu, x); }
+__device__ __forceinline__ int uniform_i32(int x) { return __reduce_max_sync(0xffffffffu, x); }
+
 // 8 nibbles of w -> 4 half2 holding channels (0,4) (1,5) (2,6) (3,7), each value the nibble exactly.
 // Low nibbles of a 16-bit half land in the mantissa of 1024 (0x6400), nibbles at bits 4-7 in the mantissa of 64
 // (0x5400, whose ulp is 1/16); subtracting the bias leaves the integer.
@@ -163,45 +171,80 @@ __device__ __forceinline__ float max3(float a, float b, float c) {
     return d;
 }
 
-// K half of one staged record -> fp16 at key offset (unit * 32) of a K tile. dt = 0..127: chunk row c = dt >> 3,
-// tokens (dt & 7) + 8 i: a quarter warp stores 8 different tokens of one chunk row (distinct banks); its 4-byte code
-// loads fall on two banks (4 wavefronts, the same as one 16-byte store).
-__device__ __forceinline__ void dequant_k(const uint8_t* raw, uint8_t* Kt, int dt) {
-    const int c = dt >> 3, tb = dt & 7;
-    const uint4 s4 = permute8(*reinterpret_cast<const uint4*>(raw + KOFF_META + c * 16));
-    const uint4 m4 = permute8(*reinterpret_cast<const uint4*>(raw + KOFF_META + 256 + c * 16));
+// Byte offset of (key, 16-byte chunk c16 of its 128 channels) inside a K or V tile.
+__device__ __forceinline__ int tile_off(int key, int c16) {
+    return (c16 >> 3) * KBLOCK + key * 128 + (((c16 & 7) ^ (key & 7)) << 4);
+}
+
+// What a dequantising thread knows about itself: warp `wg` of its group of four, half `h16` of the warp, chunk `c16`.
+// K pass p handles key 8p + 2wg + h16, V pass p key 8wg + 2p + h16: either way a warp's load covers two adjacent keys
+// (128 contiguous bytes of codes) and a quarter warp stores one key's row.
+struct DqThread {
+    int k_src, k_dst;      // pass p adds 512 / 1024
+    int v_src, v_dst;      // pass p adds 128 to v_src; v_dst: (v_dst ^ 32p) + 256p
+    int c16, wg;
+    uint32_t hsel;         // byte-permute selector that broadcasts this thread's half of a word of two fp16
+};
+__device__ __forceinline__ DqThread dq_thread(int dt) {
+    DqThread d;
+    const int lane = dt & 31, h16 = lane >> 4;
+    d.wg = dt >> 5; d.c16 = lane & 15;
+    const int kb = 2 * d.wg + h16, vb = 8 * d.wg + h16;
+    d.k_src = kb * 64 + d.c16 * 4;
+    d.k_dst = tile_off(kb, d.c16);
+    d.v_src = VOFF + vb * 64 + d.c16 * 4;
+    d.v_dst = tile_off(vb, d.c16);
+    d.hsel = h16 ? 0x3232u : 0x1010u;
+    return d;
+}
+
+// K half of one staged record -> fp16 rows of a K tile (Kt points at the unit's first key). Scale and minimum are per
+// channel: one pair of 16-byte loads per thread and record.
+__device__ __forceinline__ void dequant_k(const uint8_t* raw, uint8_t* Kt, const DqThread& d) {
+    const uint4 s4 = permute8(*reinterpret_cast<const uint4*>(raw + KOFF_META + d.c16 * 16));
+    const uint4 m4 = permute8(*reinterpret_cast<const uint4*>(raw + KOFF_META + 256 + d.c16 * 16));
     const half2* ks = reinterpret_cast<const half2*>(&s4);
     const half2* km = reinterpret_cast<const half2*>(&m4);
 #pragma unroll
-    for (int i = 0; i < 4; ++i) {
-        const int tok = tb + 8 * i;
+    for (int p = 0; p < 4; ++p) {
         half2 kh[4];
-        unpack8(*reinterpret_cast<const uint32_t*>(raw + tok * 64 + c * 4), kh);
+        unpack8(*reinterpret_cast<const uint32_t*>(raw + d.k_src + p * 512), kh);
 #pragma unroll
         for (int j = 0; j < 4; ++j) kh[j] = __hfma2(kh[j], ks[j], km[j]);
-        *reinterpret_cast<uint4*>(Kt + c * CS + tok * 16) = *reinterpret_cast<const uint4*>(kh);
+        *reinterpret_cast<uint4*>(Kt + d.k_dst + p * 1024) = *reinterpret_cast<const uint4*>(kh);
     }
 }
-// V half: scale and min per token.
-__device__ __forceinline__ void dequant_v(const uint8_t* raw, uint8_t* Vt, int dt) {
-    const int c = dt >> 3, tb = dt & 7;
-    const half* vmeta = reinterpret_cast<const half*>(raw + VOFF_META);
+// V half: scale and minimum per key; the warp's eight keys' values arrive in one broadcast 16-byte load each.
+__device__ __forceinline__ void dequant_v(const uint8_t* raw, uint8_t* Vt, const DqThread& d) {
+    const uint4 s4 = *reinterpret_cast<const uint4*>(raw + VOFF_META + d.wg * 16);
+    const uint4 m4 = *reinterpret_cast<const uint4*>(raw + VOFF_META + 2 * BLK + d.wg * 16);
+    const uint32_t* sw = reinterpret_cast<const uint32_t*>(&s4);
+    const uint32_t* mw = reinterpret_cast<const uint32_t*>(&m4);
 #pragma unroll
-    for (int i = 0; i < 4; ++i) {
-        const int tok = tb + 8 * i;
-        const half2 vs = __half2half2(vmeta[tok]), vm = __half2half2(vmeta[BLK + tok]);
+    for (int p = 0; p < 4; ++p) {
+        const uint32_t vsu = __byte_perm(sw[p], sw[p], d.hsel), vmu = __byte_perm(mw[p], mw[p], d.hsel);
+        const half2 vs = *reinterpret_cast<const half2*>(&vsu), vm = *reinterpret_cast<const half2*>(&vmu);
         half2 vh[4];
-        unpack8(*reinterpret_cast<const uint32_t*>(raw + VOFF + tok * 64 + c * 4), vh);
+        unpack8(*reinterpret_cast<const uint32_t*>(raw + d.v_src + p * 128), vh);
 #pragma unroll
         for (int j = 0; j < 4; ++j) vh[j] = __hfma2(vh[j], vs, vm);
-        *reinterpret_cast<uint4*>(Vt + c * CS + tok * 16) = *reinterpret_cast<const uint4*>(vh);
+        *reinterpret_cast<uint4*>(Vt + (d.v_dst ^ (32 * p)) + 256 * p) = *reinterpret_cast<const uint4*>(vh);
+    }
+}
+// The query block's own fp16 K or V (32 keys x 128 channels, row stride NKV * D halves) into a unit of a tile.
+__device__ __forceinline__ void copy_fresh(const half* src, uint8_t* tile_unit, int dt) {
+#pragma unroll
+    for (int k = 0; k < 4; ++k) {
+        const int idx = dt + 128 * k, tok = idx >> 4, c16 = idx & 15;
+        *reinterpret_cast<uint4*>(tile_unit + tile_off(tok, c16)) =
+            permute8(__ldg(reinterpret_cast<const uint4*>(src + size_t(tok) * NKV * D + c16 * 8)));
     }
 }
 
 // The whole CTA's work. `cta` is the CTA's index in the plan (list mode) or in the flattened reference grid
 // (kv head fastest, then chunk, then query block).
 __device__ __forceinline__ void attn_tile_body(const KParams& p, const int cta) {
-    extern __shared__ __align__(128) uint8_t smem[];
+    extern __shared__ __align__(1024) uint8_t smem[];
     uint64_t* bars = reinterpret_cast<uint64_t*>(smem + SM_BAR);
     uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(smem + SM_MISC);
     volatile int* abort_flag = reinterpret_cast<volatile int*>(smem + SM_MISC + 4);
@@ -212,6 +255,11 @@ __device__ __forceinline__ void attn_tile_body(const KParams& p, const int cta) 
     int i0, i1;
     if (p.items) { i0 = p.cta_first[cta]; i1 = p.cta_first[cta + 1]; }
     else { i0 = cta; i1 = cta + 1; }
+    const int i0_any = i0, i1_any = i1;
+    if (ptx::smem_u32(smem) & 1023u) {          // the swizzled tiles need a 1024-byte aligned base: report, do nothing
+        if (tid == 0 && p.err) atomicOr(p.err, ERR_SMEM_ALIGN);
+        return;
+    }
 
     if (tid == 0) {
         for (int i = 0; i < NRAW; ++i) { ptx::mbar_init(BAR(B_RAW_FULL + i), 1); ptx::mbar_init(BAR(B_RAW_EMPTY + i), 128); }
@@ -220,7 +268,7 @@ __device__ __forceinline__ void attn_tile_body(const KParams& p, const int cta) 
             ptx::mbar_init(BAR(B_K_FREE + i), 1); ptx::mbar_init(BAR(B_PV_DONE + i), 1);
             ptx::mbar_init(BAR(B_S_FULL + i), 1); ptx::mbar_init(BAR(B_P_FULL + i), 32 * SOFTMAX_WARPS);
         }
-        ptx::mbar_init(BAR(B_Q_FULL), 32 * DEQUANT_WARPS); ptx::mbar_init(BAR(B_O_FREE), 32 * SOFTMAX_WARPS);
+        ptx::mbar_init(BAR(B_Q_FULL), 32 * SOFTMAX_WARPS); ptx::mbar_init(BAR(B_O_FREE), 32 * SOFTMAX_WARPS);
         ptx::mbar_init(BAR(B_SPARE), 1);
         ptx::mbar_init(BAR(B_SPARE + 1), 1);
         for (int i = 0; i < 4; ++i) ptx::mbar_init(BAR(B_XCHG + i), 64);
@@ -232,6 +280,7 @@ __device__ __forceinline__ void attn_tile_body(const KParams& p, const int cta) 
     __syncthreads();
     ptx::tc_fence_after();
     const uint32_t tmem = *tmem_slot;
+    const uint32_t tmem_any = tmem;
     int errbits = 0;
 #ifdef LLATTN_TRACE
     int trace_n = 0;
@@ -252,11 +301,27 @@ __device__ __forceinline__ void attn_tile_body(const KParams& p, const int cta) 
             if (!fetch_item(p, ii, w, s)) continue;
             const int U = w.rec_count + w.fresh, ntiles = (U + TILE_UNITS - 1) / TILE_UNITS;
             float mref = -INFINITY;
+            {   // this thread's query row, channels [64 hf, 64 hf + 64), into tensor memory as fp16 pairs. Every S MMA of
+                // the previous item has completed: this warp has seen the S of its last tile.
+                const half* src = p.Q + ((size_t(s.q_first + w.qblk) * BLK + (row >> 2)) * NQH + 4 * w.kvh + (row & 3)) * D + 64 * hf;
+                uint32_t r[32];
+#pragma unroll
+                for (int g = 0; g < 8; ++g) {
+                    const uint4 v = permute8(__ldg(reinterpret_cast<const uint4*>(src + 8 * g)));
+                    r[4 * g] = v.x; r[4 * g + 1] = v.y; r[4 * g + 2] = v.z; r[4 * g + 3] = v.w;
+                }
+                ptx::tmem_st32(tlane + TM_Q + 32 * hf, r);
+                ptx::tmem_wait_st();
+                ptx::tc_fence_before();
+                ptx::mbar_arrive(BAR(B_Q_FULL));
+            }
 #pragma unroll 1
             for (int i = 0; i < ntiles; ++i, ++t) {
                 const int b = t & 1, nu = min(TILE_UNITS, U - TILE_UNITS * i);
                 const int nc = max(0, min(2, nu - 2 * hf));          // 32-key chunks of this tile this warp owns
+                LLATTN_TR(1, t);
                 if (!ptx::mbar_wait(BAR(B_S_FULL + b), (t >> 1) & 1, abort_flag)) { alive = false; errbits |= ERR_WAIT_SOFTMAX; break; }
+                LLATTN_TR(2, t);
                 ptx::tc_fence_after();
                 const uint32_t ts = tlane + TM_S + b * 128;
                 float mx = -INFINITY;
@@ -266,14 +331,19 @@ __device__ __forceinline__ void attn_tile_body(const KParams& p, const int cta) 
                     ptx::tmem_ld32(ts + 64 * hf + 32 * c, r);
                     ptx::tmem_wait_ld();
 #pragma unroll
-                    for (int j = 0; j < 32; j += 2) mx = max3(mx, __uint_as_float(r[j]), __uint_as_float(r[j + 1]));
+                    for (int j = 0; j < 32; j += 2) {
+                        if (LLATTN_SKIP & 2) { if (j == 0) mx = fmaxf(mx, __uint_as_float(r[0])); }
+                        else mx = max3(mx, __uint_as_float(r[j]), __uint_as_float(r[j + 1]));
+                    }
                 }
                 // row max over both halves: exchange through shared memory with the partner warp (double-buffered by
                 // tile parity; the pair's mbarrier, one phase per tile, orders write -> read and its wait is bounded)
+                LLATTN_TR(5, t);
                 xb[b * 256 + hf * 128 + row] = mx;
                 ptx::mbar_arrive(BAR(B_XCHG + q));
                 if (!ptx::mbar_wait(BAR(B_XCHG + q), t & 1, abort_flag)) { alive = false; errbits |= ERR_WAIT_SOFTMAX; break; }
                 mx = fmaxf(mx, xb[b * 256 + (hf ^ 1) * 128 + row]);
+                LLATTN_TR(3, t);
                 const float msc = mx * p.sl2;
                 const bool moved = msc > mref + RESCALE_SLACK;
                 if (i > 0 && __any_sync(0xffffffffu, moved)) {
@@ -308,6 +378,7 @@ __device__ __forceinline__ void attn_tile_body(const KParams& p, const int cta) 
                     ptx::tmem_wait_ld();
 #pragma unroll
                     for (int j = 0; j < 16; ++j) {
+                        if (LLATTN_SKIP & 2) { pk[j] = r[2 * j] & 0x03ff03ffu; continue; }
                         const float p0 = ex2(fmaf(__uint_as_float(r[2 * j]), p.sl2, -mref));
                         const float p1 = ex2(fmaf(__uint_as_float(r[2 * j + 1]), p.sl2, -mref));
                         const half2 h = __floats2half2_rn(p0, p1);
@@ -318,6 +389,7 @@ __device__ __forceinline__ void attn_tile_body(const KParams& p, const int cta) 
                 ptx::tmem_wait_st();
                 ptx::tc_fence_before();
                 ptx::mbar_arrive(BAR(B_P_FULL + b));
+                LLATTN_TR(4, t);
             }
             if (!alive) break;
             // ---- epilogue: un-normalised O (this warp's half of the columns), reference maximum and row sum of the run
@@ -351,37 +423,26 @@ __device__ __forceinline__ void attn_tile_body(const KParams& p, const int cta) 
             ptx::tc_fence_before();
             ptx::mbar_arrive(BAR(B_O_FREE));
         }
-    } else if (warp < WARP_PRODUCER) {
+    } else if (warp < WARP_SERVICE) {
         // ================================================================== dequant: records -> fp16 operand tiles
         const int da = tid - 32 * SOFTMAX_WARPS;      // 0..511 over the four groups
         const int grp = da >> 7, dt = da & 127;       // group g owns unit g of every tile
+        const DqThread dq = dq_thread(dt);
         uint32_t t = 0, r = 0;
-        int prev_last = -1;
         bool alive = true;
-        // chunk row 16 of both V tiles: (1, 0, 0, 0, 0, 0, 0, 0) for every key -> O column 128 accumulates sum(P);
-        // chunk row 17: zeros. Published by the first v_full arrival.
-        for (int idx = da; idx < 2 * 2 * 128; idx += 32 * DEQUANT_WARPS) {
-            const int buf = idx >> 8, rw = (idx >> 7) & 1, key = idx & 127;
-            *reinterpret_cast<uint4*>(smem + SM_V + buf * VTILE_BYTES + (16 + rw) * CS + key * 16) =
-                make_uint4(rw == 0 ? 0x00003C00u : 0u, 0u, 0u, 0u);
+        // third block of both V tiles: column 128 of V is all ones (O column 128 accumulates sum(P)), 129..143 zero.
+        // Published by the first v_full arrival.
+        for (int idx = da; idx < 2 * 128 * 8; idx += 32 * DEQUANT_WARPS) {
+            const int buf = idx >> 10, key = (idx >> 3) & 127, pos = idx & 7;
+            *reinterpret_cast<uint4*>(smem + SM_V + buf * VTILE_BYTES + 2 * KBLOCK + key * 128 + pos * 16) =
+                make_uint4(pos == (key & 7) ? 0x00003C00u : 0u, 0u, 0u, 0u);
         }
 #pragma unroll 1
         for (int ii = i0; ii < i1 && alive; ++ii) {
             WorkItem w; SeqDesc s;
             if (!fetch_item(p, ii, w, s)) continue;
             const int U = w.rec_count + w.fresh, ntiles = (U + TILE_UNITS - 1) / TILE_UNITS;
-            const size_t qg = size_t(s.q_first + w.qblk);
-            const size_t f0 = (qg * BLK) * NKV * D + size_t(w.kvh) * D;
-            if (prev_last >= 0 &&      // Q is overwritten: every S MMA of the previous item must be done
-                !ptx::mbar_wait(BAR(B_K_FREE + (prev_last & 1)), (uint32_t(prev_last) >> 1) & 1, abort_flag)) { alive = false; errbits |= ERR_WAIT_DEQUANT; break; }
-#pragma unroll
-            for (int i = 0; i < 2048 / (32 * DEQUANT_WARPS); ++i) {
-                const int idx = da + 32 * DEQUANT_WARPS * i, rw = (idx & 7) | ((idx >> 7) << 3), ch = (idx >> 3) & 15;
-                const half* src = p.Q + ((qg * BLK + (rw >> 2)) * NQH + 4 * w.kvh + (rw & 3)) * D + ch * 8;
-                *reinterpret_cast<uint4*>(smem + SM_Q + ch * CS + rw * 16) = permute8(__ldg(reinterpret_cast<const uint4*>(src)));
-            }
-            ptx::fence_proxy_async_smem();
-            ptx::mbar_arrive(BAR(B_Q_FULL));
+            const size_t f0 = (size_t(s.q_first + w.qblk) * BLK) * NKV * D + size_t(w.kvh) * D;
 #pragma unroll 1
             for (int i = 0; i < ntiles && alive; ++i, ++t) {
                 const int b = t & 1, nu = min(TILE_UNITS, U - TILE_UNITS * i);
@@ -399,14 +460,9 @@ __device__ __forceinline__ void attn_tile_body(const KParams& p, const int cta) 
                         LLATTN_TR(15, t);
                         if (!ptx::mbar_wait(BAR(B_RAW_FULL + slot), (rr / NRAW) & 1, abort_flag)) { alive = false; errbits |= ERR_WAIT_DEQUANT; break; }
                         LLATTN_TR(16, t);
-                        if (!(LLATTN_SKIP & 1)) dequant_k(smem + SM_RAW + slot * RAW_STRIDE, Kt + u * 512, dt);
+                        if (!(LLATTN_SKIP & 1)) dequant_k(smem + SM_RAW + slot * RAW_STRIDE, Kt + u * UNIT_BYTES, dq);
                     } else {          // the query block's own K, exact fp16
-#pragma unroll
-                        for (int k = 0; k < 4; ++k) {
-                            const int idx = dt + 128 * k, tok = (idx & 7) | ((idx >> 7) << 3), ch = (idx >> 3) & 15;
-                            *reinterpret_cast<uint4*>(Kt + u * 512 + ch * CS + tok * 16) =
-                                permute8(__ldg(reinterpret_cast<const uint4*>(p.Kf + f0 + size_t(tok) * NKV * D + ch * 8)));
-                        }
+                        copy_fresh(p.Kf + f0, Kt + u * UNIT_BYTES, dt);
                     }
                 }
                 if (!alive) break;
@@ -421,15 +477,10 @@ __device__ __forceinline__ void attn_tile_body(const KParams& p, const int cta) 
                     const int unit = TILE_UNITS * i + u;
                     if (unit < w.rec_count) {
                         const uint32_t slot = (r + u) % NRAW;       // landed: the K pass waited for it
-                        if (!(LLATTN_SKIP & 1)) dequant_v(smem + SM_RAW + slot * RAW_STRIDE, Vt + u * 512, dt);
+                        if (!(LLATTN_SKIP & 1)) dequant_v(smem + SM_RAW + slot * RAW_STRIDE, Vt + u * UNIT_BYTES, dq);
                         ptx::mbar_arrive(BAR(B_RAW_EMPTY + slot));
                     } else {
-#pragma unroll
-                        for (int k = 0; k < 4; ++k) {
-                            const int idx = dt + 128 * k, tok = (idx & 7) | ((idx >> 7) << 3), ch = (idx >> 3) & 15;
-                            *reinterpret_cast<uint4*>(Vt + u * 512 + ch * CS + tok * 16) =
-                                permute8(__ldg(reinterpret_cast<const uint4*>(p.Vf + f0 + size_t(tok) * NKV * D + ch * 8)));
-                        }
+                        copy_fresh(p.Vf + f0, Vt + u * UNIT_BYTES, dt);
                     }
                 }
                 ptx::fence_proxy_async_smem();
@@ -437,7 +488,6 @@ __device__ __forceinline__ void attn_tile_body(const KParams& p, const int cta) 
                 LLATTN_TR(14, t);
                 r += uint32_t(min(nu, max(0, w.rec_count - TILE_UNITS * i)));     // records of this tile (both groups count alike)
             }
-            prev_last = int(t) - 1;
         }
     } else if (warp == WARP_PRODUCER) {
         // ================================================================== producer: bulk copies of records
@@ -471,39 +521,36 @@ __device__ __forceinline__ void attn_tile_body(const KParams& p, const int cta) 
             }
         }
     } else if (warp == WARP_MMA) {
-        // ================================================================== S = Q K^T issue (lane 0 issues, the warp stays together)
+        // ================================================================== S = Q K^T issue (one elected lane issues, the warp stays together)
         // Two issuing warps (this one and the PV one below) halve the per-tile instruction chain on the critical path.
-        // Every descriptor is built once: the operands' shared-memory addresses never change.
+        // Loop bounds, tile counts and wait results are made visibly warp-uniform so that the operands of the MMAs can
+        // live in uniform registers.
         uint32_t t = 0, itc = 0;
         bool alive = true;
-        const uint32_t q_s = ptx::smem_u32(smem + SM_Q), k_s = ptx::smem_u32(smem + SM_K);
-        uint64_t qd[8], kd[2][8];        // 16 channels per K-step: K-major, chunk rows CS apart, 8-row groups 128 B apart
-#pragma unroll
-        for (int j = 0; j < 8; ++j) {
-            qd[j] = ptx::smem_desc(q_s + 2 * j * CS, CS, 128);
-            kd[0][j] = ptx::smem_desc(k_s + 2 * j * CS, CS, 128);
-            kd[1][j] = ptx::smem_desc(k_s + TILE_BYTES + 2 * j * CS, CS, 128);
-        }
+        // one base descriptor per K buffer (K-major, 128-byte swizzle, 8-row groups 1024 B apart); the issue helper steps it
+        const uint32_t k_s = ptx::smem_u32(smem + SM_K);
+        const uint32_t klo0 = ptx::desc_lo(k_s, 16), klo1 = ptx::desc_lo(k_s + TILE_BYTES, 16), khi = ptx::desc_hi(1024) | (2u << 29);
+        const uint32_t tmem = uniform_u32(tmem_any);
+        const int i0 = uniform_i32(i0_any), i1 = uniform_i32(i1_any);
 #pragma unroll 1
         for (int ii = i0; ii < i1 && alive; ++ii) {
             WorkItem w; SeqDesc s;
-            if (!fetch_item(p, ii, w, s)) continue;
-            const int U = w.rec_count + w.fresh, ntiles = (U + TILE_UNITS - 1) / TILE_UNITS;
-            if (!ptx::mbar_wait(BAR(B_Q_FULL), itc & 1, abort_flag)) { alive = false; errbits |= ERR_WAIT_MMA; break; }
+            if (!uniform_i32(fetch_item(p, ii, w, s))) continue;
+            const int U = uniform_i32(w.rec_count + w.fresh), ntiles = (U + TILE_UNITS - 1) / TILE_UNITS;
+            if (!uniform_i32(ptx::mbar_wait(BAR(B_Q_FULL), itc & 1, abort_flag))) { alive = false; errbits |= ERR_WAIT_MMA; break; }
 #pragma unroll 1
             for (int i = 0; i < ntiles; ++i, ++t) {
                 const uint32_t b = t & 1;
                 const int nu = min(TILE_UNITS, U - TILE_UNITS * i);
                 LLATTN_TR(20, t);
-                if (!ptx::mbar_wait(BAR(B_K_FULL + b), (t >> 1) & 1, abort_flag)) { alive = false; errbits |= ERR_WAIT_MMA; break; }
+                if (!uniform_i32(ptx::mbar_wait(BAR(B_K_FULL + b), (t >> 1) & 1, abort_flag))) { alive = false; errbits |= ERR_WAIT_MMA; break; }
                 // S buffer b also holds P of tile t-2: PV of that tile must have consumed it
-                if (t >= 2 && !ptx::mbar_wait(BAR(B_PV_DONE + b), ((t >> 1) - 1) & 1, abort_flag)) { alive = false; errbits |= ERR_WAIT_MMA; break; }
+                if (t >= 2 && !uniform_i32(ptx::mbar_wait(BAR(B_PV_DONE + b), ((t >> 1) - 1) & 1, abort_flag))) { alive = false; errbits |= ERR_WAIT_MMA; break; }
                 LLATTN_TR(21, t);
                 ptx::tc_fence_after();
                 {
                     const uint32_t idS = ptx::idesc_f16(128, 32 * nu, false, false), ds = tmem + TM_S + b * 128;
-                    if (b == 0) ptx::mma_ss_x8_warp(ds, qd, kd[0], idS, BAR(B_S_FULL), BAR(B_K_FREE));
-                    else ptx::mma_ss_x8_warp(ds, qd, kd[1], idS, BAR(B_S_FULL + 1), BAR(B_K_FREE + 1));
+                    ptx::mma_ts_s8_warp<KBLOCK / 16>(ds, tmem + TM_Q, b ? klo1 : klo0, khi, idS, BAR(B_S_FULL + b), BAR(B_K_FREE + b));
                 }
                 LLATTN_TR(25, t);
             }
@@ -521,38 +568,41 @@ __device__ __forceinline__ void attn_tile_body(const KParams& p, const int cta) 
         bool alive = true;
         const uint32_t v_s = ptx::smem_u32(smem + SM_V);
         const uint32_t idO = ptx::idesc_f16(128, PV_N, false, true);
-        uint64_t vd[2][8];               // 16 keys per K-step: B is MN-major, 8-key groups 128 B apart, dim groups CS apart
-#pragma unroll
-        for (int j = 0; j < 8; ++j) {
-            vd[0][j] = ptx::smem_desc(v_s + j * 256, 128, CS);
-            vd[1][j] = ptx::smem_desc(v_s + VTILE_BYTES + j * 256, 128, CS);
-        }
+        // one base descriptor per V buffer (MN-major, 128-byte swizzle: 8-key groups 1024 B apart, 64-dim blocks KBLOCK apart)
+        const uint32_t vlo0 = ptx::desc_lo(v_s, KBLOCK), vlo1 = ptx::desc_lo(v_s + VTILE_BYTES, KBLOCK), vhi = ptx::desc_hi(1024) | (2u << 29);
+        const uint32_t tmem = uniform_u32(tmem_any);
+        const int i0 = uniform_i32(i0_any), i1 = uniform_i32(i1_any);
 #pragma unroll 1
         for (int ii = i0; ii < i1 && alive; ++ii) {
             WorkItem w; SeqDesc s;
-            if (!fetch_item(p, ii, w, s)) continue;
-            const int U = w.rec_count + w.fresh, ntiles = (U + TILE_UNITS - 1) / TILE_UNITS;
+            if (!uniform_i32(fetch_item(p, ii, w, s))) continue;
+            const int U = uniform_i32(w.rec_count + w.fresh), ntiles = (U + TILE_UNITS - 1) / TILE_UNITS;
 #pragma unroll 1
             for (int i = 0; i < ntiles; ++i, ++t) {
                 const uint32_t b = t & 1;
                 const int nu = min(TILE_UNITS, U - TILE_UNITS * i);
                 LLATTN_TR(22, t);
-                if (!ptx::mbar_wait(BAR(B_V_FULL + b), (t >> 1) & 1, abort_flag)) { alive = false; errbits |= ERR_WAIT_MMA; break; }
+                if (!uniform_i32(ptx::mbar_wait(BAR(B_V_FULL + b), (t >> 1) & 1, abort_flag))) { alive = false; errbits |= ERR_WAIT_MMA; break; }
                 LLATTN_TR(23, t);
-                if (!ptx::mbar_wait(BAR(B_P_FULL + b), (t >> 1) & 1, abort_flag)) { alive = false; errbits |= ERR_WAIT_MMA; break; }
+                if (!uniform_i32(ptx::mbar_wait(BAR(B_P_FULL + b), (t >> 1) & 1, abort_flag))) { alive = false; errbits |= ERR_WAIT_MMA; break; }
                 LLATTN_TR(24, t);
                 // the previous item's epilogue must have read O before the first PV of this item overwrites it
-                if (i == 0 && itc > 0 && !ptx::mbar_wait(BAR(B_O_FREE), (itc - 1) & 1, abort_flag)) { alive = false; errbits |= ERR_WAIT_MMA; break; }
+                if (i == 0 && itc > 0 && !uniform_i32(ptx::mbar_wait(BAR(B_O_FREE), (itc - 1) & 1, abort_flag))) { alive = false; errbits |= ERR_WAIT_MMA; break; }
                 ptx::tc_fence_after();
                 {
                     // unit u = keys 32u..32u+31 = K-steps 2u, 2u+1; its P sits at columns (u >> 1) * 64 + (u & 1) * 16 of the S buffer
-                    const uint32_t pb = tmem + TM_S + b * 128;
+                    const uint32_t pb = tmem + TM_S + b * 128, vlo = b ? vlo1 : vlo0;
+                    if (nu == TILE_UNITS) {
+                        ptx::mma_ts_pv8_warp(tmem + TM_O, pb, vlo, vhi, idO, i == 0 ? 0u : 1u, BAR(B_PV_DONE + b));
+                    } else {
 #pragma unroll
-                    for (int u = 0; u < TILE_UNITS; ++u)
-                        if (u < nu)
-                            ptx::mma_ts_x2_warp(tmem + TM_O, pb + (u >> 1) * 64 + (u & 1) * 16, b ? vd[1][2 * u] : vd[0][2 * u],
-                                                b ? vd[1][2 * u + 1] : vd[0][2 * u + 1], idO, (i == 0 && u == 0) ? 0u : 1u);
-                    ptx::mma_commit_warp(BAR(B_PV_DONE + b));
+                        for (int u = 0; u < TILE_UNITS - 1; ++u)
+                            if (u < nu) {
+                                const uint64_t d0 = (uint64_t(vhi) << 32) | (vlo + 256u * u);
+                                ptx::mma_ts_x2_warp(tmem + TM_O, pb + (u >> 1) * 64 + (u & 1) * 16, d0, d0 + 128, idO, (i == 0 && u == 0) ? 0u : 1u);
+                            }
+                        ptx::mma_commit_warp(BAR(B_PV_DONE + b));
+                    }
                 }
                 LLATTN_TR(26, t);
             }

@@ -50,8 +50,11 @@ __device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity) {
 }
 
 // Bounded wait for the phase with the given parity. `abort_flag` (shared memory) lets one role's time-out release
-// every other role that is waiting. Returns false on time-out or abort.
+// every other role that is waiting. Returns false on time-out or abort. A phase that is already complete costs one
+// non-blocking test; otherwise the hardware suspends the thread inside try_wait until the phase completes (the loop
+// body runs about once per wait), and the clock is read every 64 rounds.
 __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile int* abort_flag) {
+    if (mbar_try_wait(bar, parity)) return true;
     uint32_t ok;
     unsigned long long t0 = 0;
     for (uint32_t it = 0;; ++it) {
@@ -148,6 +151,14 @@ __device__ __forceinline__ uint64_t smem_desc(uint32_t saddr, uint32_t lbo_bytes
     return uint64_t((saddr & 0x3ffffu) >> 4) | (uint64_t(lbo_bytes >> 4) << 16) | (uint64_t(sbo_bytes >> 4) << 32) |
            (uint64_t(1) << 46);
 }
+// The same with the 128-byte swizzle: rows of 128 bytes, the 16-byte chunk c of row r stored at chunk position
+// c ^ (r % 8), tile base 1024-byte aligned. K-major operand (row = M/N index, 64 fp16 of K per row): sbo = 1024 (next
+// 8 rows), lbo unused, a K-step of 16 elements advances the start address by 32 bytes. MN-major operand (row = K index,
+// 64 fp16 of N per row): sbo = 1024 (next 8 K rows), lbo = distance between 64-element column blocks of N, a K-step
+// advances by 16 rows. Both conventions were checked against a CPU product on the device.
+__device__ __forceinline__ uint64_t smem_desc_sw128(uint32_t saddr, uint32_t lbo_bytes, uint32_t sbo_bytes) {
+    return smem_desc(saddr, lbo_bytes, sbo_bytes) | (uint64_t(2) << 61);
+}
 // Instruction descriptor for kind::f16 with fp16 A and B, fp32 accumulate, M x N tile, no negate, dense.
 __host__ __device__ constexpr uint32_t idesc_f16(int M, int N, bool a_mn_major, bool b_mn_major) {
     return (1u << 4) | (uint32_t(a_mn_major) << 15) | (uint32_t(b_mn_major) << 16) | (uint32_t(N >> 3) << 17) |
@@ -174,91 +185,69 @@ __device__ __forceinline__ uint32_t desc_lo(uint32_t saddr, uint32_t lbo_bytes) 
 }
 __host__ __device__ constexpr uint32_t desc_hi(uint32_t sbo_bytes) { return (sbo_bytes >> 4) | (1u << 14); }
 
-// Eight back-to-back K-steps of D[tmem] = A[smem] * B[smem] (first step overwrites D, the rest accumulate). Both
-// operands advance by `step16` 16-byte units per step. One asm block: a few instructions per MMA on the issuing thread.
-__device__ __forceinline__ void mma_ss_x8(uint32_t d_tmem, uint32_t alo, uint32_t ahi, uint32_t blo, uint32_t bhi,
-                                          uint32_t idesc, uint32_t step16) {
-    asm volatile(
-        "{\n\t"
-        ".reg .pred pf, pt;\n\t"
-        ".reg .b32 al, bl;\n\t"
-        ".reg .b64 da, db;\n\t"
-        "setp.ne.b32 pf, 0, 0;\n\t"
-        "setp.eq.b32 pt, 0, 0;\n\t"
-        "mov.b64 da, {%1, %2};\n\t"
-        "mov.b64 db, {%3, %4};\n\t"
-        "tcgen05.mma.cta_group::1.kind::f16 [%0], da, db, %5, pf;\n\t"
-        "add.u32 al, %1, %6;\n\t add.u32 bl, %3, %6;\n\t mov.b64 da, {al, %2};\n\t mov.b64 db, {bl, %4};\n\t"
-        "tcgen05.mma.cta_group::1.kind::f16 [%0], da, db, %5, pt;\n\t"
-        "add.u32 al, al, %6;\n\t add.u32 bl, bl, %6;\n\t mov.b64 da, {al, %2};\n\t mov.b64 db, {bl, %4};\n\t"
-        "tcgen05.mma.cta_group::1.kind::f16 [%0], da, db, %5, pt;\n\t"
-        "add.u32 al, al, %6;\n\t add.u32 bl, bl, %6;\n\t mov.b64 da, {al, %2};\n\t mov.b64 db, {bl, %4};\n\t"
-        "tcgen05.mma.cta_group::1.kind::f16 [%0], da, db, %5, pt;\n\t"
-        "add.u32 al, al, %6;\n\t add.u32 bl, bl, %6;\n\t mov.b64 da, {al, %2};\n\t mov.b64 db, {bl, %4};\n\t"
-        "tcgen05.mma.cta_group::1.kind::f16 [%0], da, db, %5, pt;\n\t"
-        "add.u32 al, al, %6;\n\t add.u32 bl, bl, %6;\n\t mov.b64 da, {al, %2};\n\t mov.b64 db, {bl, %4};\n\t"
-        "tcgen05.mma.cta_group::1.kind::f16 [%0], da, db, %5, pt;\n\t"
-        "add.u32 al, al, %6;\n\t add.u32 bl, bl, %6;\n\t mov.b64 da, {al, %2};\n\t mov.b64 db, {bl, %4};\n\t"
-        "tcgen05.mma.cta_group::1.kind::f16 [%0], da, db, %5, pt;\n\t"
-        "add.u32 al, al, %6;\n\t add.u32 bl, bl, %6;\n\t mov.b64 da, {al, %2};\n\t mov.b64 db, {bl, %4};\n\t"
-        "tcgen05.mma.cta_group::1.kind::f16 [%0], da, db, %5, pt;\n\t"
-        "}\n"
-        :: "r"(d_tmem), "r"(alo), "r"(ahi), "r"(blo), "r"(bhi), "r"(idesc), "r"(step16) : "memory");
-}
-// Two K-steps (32 keys = one KV unit) of D[tmem] (+)= A[tmem] * B[smem]: A advances 8 TMEM columns, B `step16` units.
-__device__ __forceinline__ void mma_ts_x2(uint32_t d_tmem, uint32_t a_tmem, uint32_t blo, uint32_t bhi, uint32_t idesc,
-                                          uint32_t step16, uint32_t accumulate_first) {
-    asm volatile(
-        "{\n\t"
-        ".reg .pred pa, pt;\n\t"
-        ".reg .b32 bl, at;\n\t"
-        ".reg .b64 db;\n\t"
-        "setp.ne.b32 pa, %6, 0;\n\t"
-        "setp.eq.b32 pt, 0, 0;\n\t"
-        "mov.b64 db, {%2, %3};\n\t"
-        "tcgen05.mma.cta_group::1.kind::f16 [%0], [%1], db, %4, pa;\n\t"
-        "add.u32 bl, %2, %5;\n\t add.u32 at, %1, 8;\n\t mov.b64 db, {bl, %3};\n\t"
-        "tcgen05.mma.cta_group::1.kind::f16 [%0], [at], db, %4, pt;\n\t"
-        "}\n"
-        :: "r"(d_tmem), "r"(a_tmem), "r"(blo), "r"(bhi), "r"(idesc), "r"(step16), "r"(accumulate_first) : "memory");
-}
-// Single MMAs with ready-made 64-bit descriptors and a compile-time accumulate flag: nothing but the predicate set-up
-// and the MMA itself on the issuing thread.
-template <bool kAccumulate>
-__device__ __forceinline__ void mma_ss_d(uint32_t d_tmem, uint64_t adesc, uint64_t bdesc, uint32_t idesc) {
-    if (kAccumulate)
-        asm volatile("{\n\t.reg .pred p;\n\tsetp.eq.b32 p, 0, 0;\n\ttcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n\t}\n"
-                     :: "r"(d_tmem), "l"(adesc), "l"(bdesc), "r"(idesc) : "memory");
-    else
-        asm volatile("{\n\t.reg .pred p;\n\tsetp.ne.b32 p, 0, 0;\n\ttcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n\t}\n"
-                     :: "r"(d_tmem), "l"(adesc), "l"(bdesc), "r"(idesc) : "memory");
-}
-__device__ __forceinline__ void mma_ts_d(uint32_t d_tmem, uint32_t a_tmem, uint64_t bdesc, uint32_t idesc, uint32_t accumulate) {
-    asm volatile("{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\ttcgen05.mma.cta_group::1.kind::f16 [%0], [%1], %2, %3, p;\n\t}\n"
-                 :: "r"(d_tmem), "r"(a_tmem), "l"(bdesc), "r"(idesc), "r"(accumulate) : "memory");
-}
 // Whole-warp issue helpers: every lane executes them (uniform control flow, so the operands can live in uniform
-// registers); one elected lane issues. Eight K-steps of D = A[smem] * B[smem] with ready-made descriptors, then the
-// commits that publish completion.
-__device__ __forceinline__ void mma_ss_x8_warp(uint32_t d_tmem, const uint64_t (&a)[8], const uint64_t (&b)[8], uint32_t idesc,
+// registers); one elected lane issues. Each works from one base descriptor and steps its address field, so the issuing
+// warp carries two words per operand tile, not eight descriptors (its instructions sit on the kernel's critical cycle).
+//
+// S = Q K^T, eight K-steps of 16 channels: A advances 8 TMEM columns per step; step j reads block j / 4 of the K tile,
+// 32 bytes (2 units of 16) further along the 128-byte rows per step (kBlock16 = block size / 16). Two commits.
+template <uint32_t kBlock16>
+__device__ __forceinline__ void mma_ts_s8_warp(uint32_t d_tmem, uint32_t a_tmem, uint32_t b_lo, uint32_t b_hi, uint32_t idesc,
                                                uint32_t bar1, uint32_t bar2) {
     asm volatile(
-        "{\n\t.reg .pred pe, pf, pt;\n\t"
+        "{\n\t.reg .pred pe, pf, pt;\n\t.reg .b32 a, l;\n\t.reg .b64 db;\n\t"
         "elect.sync _|pe, 0xffffffff;\n\t"
         "setp.ne.b32 pf, 0, 0;\n\t setp.eq.b32 pt, 0, 0;\n\t"
-        "@pe tcgen05.mma.cta_group::1.kind::f16 [%0], %2, %10, %1, pf;\n\t"
-        "@pe tcgen05.mma.cta_group::1.kind::f16 [%0], %3, %11, %1, pt;\n\t"
-        "@pe tcgen05.mma.cta_group::1.kind::f16 [%0], %4, %12, %1, pt;\n\t"
-        "@pe tcgen05.mma.cta_group::1.kind::f16 [%0], %5, %13, %1, pt;\n\t"
-        "@pe tcgen05.mma.cta_group::1.kind::f16 [%0], %6, %14, %1, pt;\n\t"
-        "@pe tcgen05.mma.cta_group::1.kind::f16 [%0], %7, %15, %1, pt;\n\t"
-        "@pe tcgen05.mma.cta_group::1.kind::f16 [%0], %8, %16, %1, pt;\n\t"
-        "@pe tcgen05.mma.cta_group::1.kind::f16 [%0], %9, %17, %1, pt;\n\t"
-        "@pe tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%18];\n\t"
-        "@pe tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%19];\n\t"
+        "mov.b64 db, {%3, %4};\n\t"
+        "@pe tcgen05.mma.cta_group::1.kind::f16 [%0], [%2], db, %1, pf;\n\t"
+        "add.u32 a, %2, 8;\n\t add.u32 l, %3, 2;\n\t mov.b64 db, {l, %4};\n\t"
+        "@pe tcgen05.mma.cta_group::1.kind::f16 [%0], [a], db, %1, pt;\n\t"
+        "add.u32 a, %2, 16;\n\t add.u32 l, %3, 4;\n\t mov.b64 db, {l, %4};\n\t"
+        "@pe tcgen05.mma.cta_group::1.kind::f16 [%0], [a], db, %1, pt;\n\t"
+        "add.u32 a, %2, 24;\n\t add.u32 l, %3, 6;\n\t mov.b64 db, {l, %4};\n\t"
+        "@pe tcgen05.mma.cta_group::1.kind::f16 [%0], [a], db, %1, pt;\n\t"
+        "add.u32 a, %2, 32;\n\t add.u32 l, %3, %7;\n\t mov.b64 db, {l, %4};\n\t"
+        "@pe tcgen05.mma.cta_group::1.kind::f16 [%0], [a], db, %1, pt;\n\t"
+        "add.u32 a, %2, 40;\n\t add.u32 l, %3, %8;\n\t mov.b64 db, {l, %4};\n\t"
+        "@pe tcgen05.mma.cta_group::1.kind::f16 [%0], [a], db, %1, pt;\n\t"
+        "add.u32 a, %2, 48;\n\t add.u32 l, %3, %9;\n\t mov.b64 db, {l, %4};\n\t"
+        "@pe tcgen05.mma.cta_group::1.kind::f16 [%0], [a], db, %1, pt;\n\t"
+        "add.u32 a, %2, 56;\n\t add.u32 l, %3, %10;\n\t mov.b64 db, {l, %4};\n\t"
+        "@pe tcgen05.mma.cta_group::1.kind::f16 [%0], [a], db, %1, pt;\n\t"
+        "@pe tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%5];\n\t"
+        "@pe tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%6];\n\t"
         "}\n"
-        :: "r"(d_tmem), "r"(idesc), "l"(a[0]), "l"(a[1]), "l"(a[2]), "l"(a[3]), "l"(a[4]), "l"(a[5]), "l"(a[6]), "l"(a[7]),
-           "l"(b[0]), "l"(b[1]), "l"(b[2]), "l"(b[3]), "l"(b[4]), "l"(b[5]), "l"(b[6]), "l"(b[7]), "r"(bar1), "r"(bar2)
+        :: "r"(d_tmem), "r"(idesc), "r"(a_tmem), "r"(b_lo), "r"(b_hi), "r"(bar1), "r"(bar2),
+           "n"(kBlock16), "n"(kBlock16 + 2), "n"(kBlock16 + 4), "n"(kBlock16 + 6)
+        : "memory");
+}
+// O (+)= P V over a full tile of four 32-key units from one base descriptor: K-step j (16 keys) adds 128 16-byte units;
+// the P of unit u sits at columns (u >> 1) * 64 + (u & 1) * 16 of the S buffer, 8 columns per K-step. One commit.
+__device__ __forceinline__ void mma_ts_pv8_warp(uint32_t d_tmem, uint32_t p_tmem, uint32_t b_lo, uint32_t b_hi, uint32_t idesc,
+                                                uint32_t accumulate_first, uint32_t bar) {
+    asm volatile(
+        "{\n\t.reg .pred pe, pa, pt;\n\t.reg .b32 a, l;\n\t.reg .b64 db;\n\t"
+        "elect.sync _|pe, 0xffffffff;\n\t"
+        "setp.ne.b32 pa, %5, 0;\n\t setp.eq.b32 pt, 0, 0;\n\t"
+        "mov.b64 db, {%2, %3};\n\t"
+        "@pe tcgen05.mma.cta_group::1.kind::f16 [%0], [%1], db, %4, pa;\n\t"
+        "add.u32 a, %1, 8;\n\t add.u32 l, %2, 128;\n\t mov.b64 db, {l, %3};\n\t"
+        "@pe tcgen05.mma.cta_group::1.kind::f16 [%0], [a], db, %4, pt;\n\t"
+        "add.u32 a, %1, 16;\n\t add.u32 l, %2, 256;\n\t mov.b64 db, {l, %3};\n\t"
+        "@pe tcgen05.mma.cta_group::1.kind::f16 [%0], [a], db, %4, pt;\n\t"
+        "add.u32 a, %1, 24;\n\t add.u32 l, %2, 384;\n\t mov.b64 db, {l, %3};\n\t"
+        "@pe tcgen05.mma.cta_group::1.kind::f16 [%0], [a], db, %4, pt;\n\t"
+        "add.u32 a, %1, 64;\n\t add.u32 l, %2, 512;\n\t mov.b64 db, {l, %3};\n\t"
+        "@pe tcgen05.mma.cta_group::1.kind::f16 [%0], [a], db, %4, pt;\n\t"
+        "add.u32 a, %1, 72;\n\t add.u32 l, %2, 640;\n\t mov.b64 db, {l, %3};\n\t"
+        "@pe tcgen05.mma.cta_group::1.kind::f16 [%0], [a], db, %4, pt;\n\t"
+        "add.u32 a, %1, 80;\n\t add.u32 l, %2, 768;\n\t mov.b64 db, {l, %3};\n\t"
+        "@pe tcgen05.mma.cta_group::1.kind::f16 [%0], [a], db, %4, pt;\n\t"
+        "add.u32 a, %1, 88;\n\t add.u32 l, %2, 896;\n\t mov.b64 db, {l, %3};\n\t"
+        "@pe tcgen05.mma.cta_group::1.kind::f16 [%0], [a], db, %4, pt;\n\t"
+        "@pe tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%6];\n\t"
+        "}\n"
+        :: "r"(d_tmem), "r"(p_tmem), "r"(b_lo), "r"(b_hi), "r"(idesc), "r"(accumulate_first), "r"(bar)
         : "memory");
 }
 // Two K-steps (one 32-key unit) of D (+)= A[tmem] * B[smem]; A advances 8 TMEM columns.
