@@ -165,6 +165,19 @@ __device__ __forceinline__ float ex2(float x) {
     return y;
 }
 
+// Two fp32 multiply-adds in one instruction (sm_100 packed fp32): (a0, a1) * (b, b) + (c, c), each rounded like fmaf.
+__device__ __forceinline__ void fma2(uint32_t a0, uint32_t a1, unsigned long long bb, unsigned long long cc, float& d0, float& d1) {
+    unsigned long long a, d;
+    asm("mov.b64 %0, {%1, %2};" : "=l"(a) : "r"(a0), "r"(a1));
+    asm("fma.rn.f32x2 %0, %1, %2, %3;" : "=l"(d) : "l"(a), "l"(bb), "l"(cc));
+    asm("mov.b64 {%0, %1}, %2;" : "=f"(d0), "=f"(d1) : "l"(d));
+}
+__device__ __forceinline__ unsigned long long dup2(float x) {
+    unsigned long long d;
+    asm("mov.b64 %0, {%1, %1};" : "=l"(d) : "f"(x));
+    return d;
+}
+
 __device__ __forceinline__ float max3(float a, float b, float c) {
     float d;
     asm("max.f32 %0, %1, %2, %3;" : "=f"(d) : "f"(a), "f"(b), "f"(c));
@@ -371,6 +384,7 @@ __device__ __forceinline__ void attn_tile_body(const KParams& p, const int cta) 
                     ptx::tmem_wait_st();
                 }
                 if (moved) mref = msc;
+                const unsigned long long sl2x2 = dup2(p.sl2), nmx2 = dup2(-mref);
 #pragma unroll 1
                 for (int c = 0; c < nc; ++c) {
                     uint32_t r[32], pk[16];
@@ -379,9 +393,9 @@ __device__ __forceinline__ void attn_tile_body(const KParams& p, const int cta) 
 #pragma unroll
                     for (int j = 0; j < 16; ++j) {
                         if (LLATTN_SKIP & 2) { pk[j] = r[2 * j] & 0x03ff03ffu; continue; }
-                        const float p0 = ex2(fmaf(__uint_as_float(r[2 * j]), p.sl2, -mref));
-                        const float p1 = ex2(fmaf(__uint_as_float(r[2 * j + 1]), p.sl2, -mref));
-                        const half2 h = __floats2half2_rn(p0, p1);
+                        float x0, x1;
+                        fma2(r[2 * j], r[2 * j + 1], sl2x2, nmx2, x0, x1);
+                        const half2 h = __floats2half2_rn(ex2(x0), ex2(x1));
                         pk[j] = *reinterpret_cast<const uint32_t*>(&h);
                     }
                     ptx::tmem_st16(ts + 64 * hf + 16 * c, pk);      // P chunk over S columns this warp has already consumed
