@@ -238,6 +238,22 @@ def test_ragged_batch_and_forced_splits(api, ctx, orc, pkg):
         assert np.abs(res["LSE"] - Lw).max() <= TOL_LSE
 
 
+def test_many_short_items_per_cta(api, ctx, orc, pkg):
+    """48 short sequences on 5 CTAs: every CTA walks about 40 items, so the per-item hand-overs (query rows into tensor
+    memory, accumulator release, partial slots) run back to back, with tiles of 1 to 4 units."""
+    lens = [(7 * i) % 12 for i in range(48)]
+    cases = []
+    for i, n in enumerate(lens):
+        Q, Kf, Vf, cache, maxb = make_case(pkg.workload, orc, n, seq=300 + i)
+        cases.append((Q, Kf, Vf, cache, maxb, n))
+    res = run_batched(api, ctx, cases, nctas=5)
+    for i, c in enumerate(cases):
+        Ow, Lw = orc.attention(c[0], c[1], c[2], c[3], c[4], c[5], dq_mode=1)
+        sl = slice(i * 32, (i + 1) * 32)
+        assert relmax(res["O32"][sl], Ow) <= tol_o(lens[i]), i
+        assert np.abs(res["LSE"][sl] - Lw).max() <= TOL_LSE, i
+
+
 def test_paged_cache(api, ctx, orc, pkg):
     n = 21
     Q, Kf, Vf, cache, maxb = make_case(pkg.workload, orc, n, seq=77)
