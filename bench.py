@@ -67,14 +67,45 @@ def peaks():
 
 
 class ClockSampler:
-    """Samples nvidia-smi clocks and throttle reasons every 50 ms while the timed region runs."""
+    """SM clock and throttle reasons of one GPU while the timed region runs (read-only queries). NVML in a thread every
+    10 ms when the binding is there (the timed region is a fraction of a second), else nvidia-smi every 50 ms."""
     Q = ("index,clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.active,clocks_event_reasons.hw_slowdown,"
          "clocks_event_reasons.hw_thermal_slowdown,clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
+    REASON_BITS = ((0x8, "hw_slowdown"), (0x40, "hw_thermal_slowdown"), (0x20, "sw_thermal_slowdown"), (0x4, "sw_power_cap"))
 
-    def __init__(self, index: int):
-        self.index, self.proc, self.lines = index, None, []
+    def __init__(self, index: int, pci_bus_id: str | None = None):
+        self.index, self.pci, self.proc, self.lines = index, pci_bus_id, None, []
+        self.nvml, self.handle, self.stop_flag, self.samples, self.max_mhz = None, None, False, [], None
+
+    def _nvml_open(self) -> bool:
+        try:
+            import pynvml
+            pynvml.nvmlInit()
+            self.handle = (pynvml.nvmlDeviceGetHandleByPciBusId(self.pci.encode()) if self.pci
+                           else pynvml.nvmlDeviceGetHandleByIndex(self.index))
+            self.max_mhz = float(pynvml.nvmlDeviceGetMaxClockInfo(self.handle, pynvml.NVML_CLOCK_SM))
+            pynvml.nvmlDeviceGetClockInfo(self.handle, pynvml.NVML_CLOCK_SM)
+            self.nvml = pynvml
+            return True
+        except Exception:
+            self.nvml = None
+            return False
+
+    def _nvml_loop(self):
+        n = self.nvml
+        reasons_fn = getattr(n, "nvmlDeviceGetCurrentClocksEventReasons", None) or getattr(n, "nvmlDeviceGetCurrentClocksThrottleReasons")
+        while not self.stop_flag:
+            try:
+                self.samples.append((float(n.nvmlDeviceGetClockInfo(self.handle, n.NVML_CLOCK_SM)), int(reasons_fn(self.handle))))
+            except Exception:
+                pass
+            time.sleep(0.01)
 
     def start(self):
+        if self._nvml_open():
+            self.th = threading.Thread(target=self._nvml_loop, daemon=True)
+            self.th.start()
+            return
         try:
             self.proc = subprocess.Popen(["nvidia-smi", f"--query-gpu={self.Q}", "--format=csv,noheader,nounits", "-lms", "50",
                                           "-i", str(self.index)], stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
@@ -88,6 +119,15 @@ class ClockSampler:
             self.lines.append(ln.strip())
 
     def stop(self):
+        if self.nvml:
+            self.stop_flag = True
+            self.th.join(timeout=2)
+            sm = [c for c, _ in self.samples]
+            bits = 0
+            for _, r in self.samples:
+                bits |= r
+            return {"sm_mhz": statistics.median(sm) if sm else None, "sm_max_mhz": self.max_mhz,
+                    "reasons": sorted(name for bit, name in self.REASON_BITS if bits & bit), "samples": len(sm), "source": "nvml"}
         if not self.proc:
             return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
         self.proc.terminate()
@@ -108,7 +148,7 @@ class ClockSampler:
                 if v.lower().startswith("active"):
                     reasons.add(name)
         return {"sm_mhz": statistics.median(sm) if sm else None, "sm_max_mhz": max(mx) if mx else None,
-                "reasons": sorted(reasons), "samples": len(sm)}
+                "reasons": sorted(reasons), "samples": len(sm), "source": "nvidia-smi"}
 
 
 # ------------------------------------------------------------------------------------------------ CPU arm
@@ -245,7 +285,12 @@ def run_ours(a):
         for _ in range(max(a.warmup, 3)):
             run()
     barrier()
-    sampler = ClockSampler(local)
+    try:      # NVML numbers GPUs physically; the PCI address names this rank's device whatever CUDA_VISIBLE_DEVICES says
+        pr = torch.cuda.get_device_properties(local)
+        pci = "%08X:%02X:%02X.0" % (pr.pci_domain_id, pr.pci_bus_id, pr.pci_device_id)
+    except AttributeError:
+        pci = None
+    sampler = ClockSampler(local, pci)
     if rank == 0:
         sampler.start()
     e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)

@@ -1,7 +1,7 @@
 """Generates the golden fixtures of this folder by importing the REFERENCE's own simulated quantiser.
 
 Run in a container that has the reference checkout (it cannot run on the GPU box):
-    PYTHONDONTWRITEBYTECODE=1 python tests/golden/make_golden.py --ref /root/reference
+    PYTHONDONTWRITEBYTECODE=1 python tests/golden/make_golden.py --ref <reference checkout>
 
 What it writes (small, committed):
   fakequant_cases.npz  fp16 K/V blocks (seeded + hand-made edge groups) and, for each, the fp32 output of the
