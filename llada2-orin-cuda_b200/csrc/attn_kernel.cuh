@@ -457,8 +457,36 @@ __device__ __forceinline__ void attn_tile_body(const KParams& p, const int cta) 
             if (!fetch_item(p, ii, w, s)) continue;
             const int U = w.rec_count + w.fresh, ntiles = (U + TILE_UNITS - 1) / TILE_UNITS;
             const size_t f0 = (size_t(s.q_first + w.qblk) * BLK) * NKV * D + size_t(w.kvh) * D;
+            int i = 0;
+            // ---- steady state: tiles made of four committed records. This group's unit is always there, nothing is
+            // decided per tile, and the loop carries only what changes (tile count, record count).
+            const int nfull = DEQUANT_GROUPS == TILE_UNITS ? w.rec_count / TILE_UNITS : 0;
 #pragma unroll 1
-            for (int i = 0; i < ntiles && alive; ++i, ++t) {
+            for (; i < nfull; ++i, ++t) {
+                const uint32_t b = t & 1, freed = ((t >> 1) - 1) & 1;      // phase in which tile t-2 let go of its buffers
+                const uint32_t rr = r + grp, slot = rr % NRAW;
+                const uint8_t* raw = smem + SM_RAW + slot * RAW_STRIDE;
+                LLATTN_TR(10, t);
+                if (t >= 2 && !ptx::mbar_wait(BAR(B_K_FREE + b), freed, abort_flag)) { alive = false; errbits |= ERR_WAIT_DEQUANT; break; }
+                LLATTN_TR(15, t);
+                if (!ptx::mbar_wait(BAR(B_RAW_FULL + slot), (rr / NRAW) & 1, abort_flag)) { alive = false; errbits |= ERR_WAIT_DEQUANT; break; }
+                LLATTN_TR(16, t);
+                if (!(LLATTN_SKIP & 1)) dequant_k(raw, smem + SM_K + b * TILE_BYTES + grp * UNIT_BYTES, dq);
+                ptx::fence_proxy_async_smem();
+                ptx::mbar_arrive(BAR(B_K_FULL + b));
+                LLATTN_TR(12, t);
+                if (t >= 2 && !ptx::mbar_wait(BAR(B_PV_DONE + b), freed, abort_flag)) { alive = false; errbits |= ERR_WAIT_DEQUANT; break; }
+                LLATTN_TR(13, t);
+                if (!(LLATTN_SKIP & 1)) dequant_v(raw, smem + SM_V + b * VTILE_BYTES + grp * UNIT_BYTES, dq);
+                ptx::mbar_arrive(BAR(B_RAW_EMPTY + slot));
+                ptx::fence_proxy_async_smem();
+                ptx::mbar_arrive(BAR(B_V_FULL + b));
+                LLATTN_TR(14, t);
+                r += TILE_UNITS;
+            }
+            // ---- the run's last tile: fewer than four records and / or the query block's own K/V
+#pragma unroll 1
+            for (; i < ntiles && alive; ++i, ++t) {
                 const int b = t & 1, nu = min(TILE_UNITS, U - TILE_UNITS * i);
                 uint8_t* Kt = smem + SM_K + b * TILE_BYTES;
                 uint8_t* Vt = smem + SM_V + b * VTILE_BYTES;
