@@ -73,6 +73,19 @@ int llattn_kv_commit_paged(const void* Kf, const void* Vf, void* pool, const int
 int llattn_qk_norm_rope(const float* qkv, const int32_t* pos, const float* gq, const float* gk, float eps,
                         const float* inv_freq, void* q, void* k, void* v, int T, void* stream);
 
+/* ---- consumer of the attention output: the dense projection on the int8 `Act` the merge kernel writes.
+ * Stands in for Engine::gemm<4, 2>(Ly.dense, items_dense, ..., oA.a, ones, HID, HID, nullptr, h, 1, 2)
+ * (engine/engine.cu:434 -> moe8::gemm<4, 4, 2, 2>, engine/moe_i8.cu:295-442) for any number of tokens:
+ *   Y[n][r] += sum over the K/128 groups g, ascending, of (s_w[r][g] * s[n][g]) * float(P - z[r][g] * sum[n][g]),
+ * P the exact integer dot product of the group's 4-bit weight codes and int8 activations. W: `rows / 16` strips in the
+ * reference's device layout (per strip the K/128 code tiles of 1024 bytes, then the K/128 metas of 48 bytes,
+ * engine/moe_i8.cu:34-41 after relayout_strips); q [ntokens][K] int8 in fragment order inside every 128-group,
+ * s and sum [ntokens][K/128] (the moe8::Act triple, engine/moe_i8.cu:55-66); Y [ntokens][rows] fp32. rows and K are
+ * multiples of 128. Same float operations in the same order as the reference kernel: bit-identical results.
+ * err_word: device int for a wait that ran out, or NULL. */
+int llattn_dense_w4a8(const void* W, const int8_t* q, const float* s, const int32_t* sum, float* Y, int ntokens, int rows, int K,
+                      int* err_word, void* stream);
+
 /* ---- the reference operator pair on caller-owned buffers.
  * llattn_args mirrors attn::Args (engine/attn.cu:51-64) field for field. */
 typedef struct llattn_args {

@@ -27,7 +27,7 @@ EXPORTS = (
     "llattn_kv_commit_paged", "llattn_qk_norm_rope", "llattn_attn_partial", "llattn_attn_combine", "llattn_create", "llattn_destroy",
     "llattn_plan_create", "llattn_plan_destroy", "llattn_plan_get_stats", "llattn_plan_preview", "llattn_attention",
     "llattn_attention_parts", "llattn_attention_host", "llattn_host_flush", "llattn_device_status",
-    "llattn_kvpool_create", "llattn_kvpool_destroy", "llattn_kvpool_open", "llattn_kvpool_append", "llattn_kvpool_pages",
+    "llattn_dense_w4a8", "llattn_kvpool_create", "llattn_kvpool_destroy", "llattn_kvpool_open", "llattn_kvpool_append", "llattn_kvpool_pages",
     "llattn_kvpool_close", "llattn_kvpool_stats", "llattn_attention_static",
 )
 
@@ -92,6 +92,7 @@ def lib() -> ctypes.CDLL:
         L.llattn_attention_parts.argtypes = [c_void_p, c_void_p, POINTER(_IO), c_int, c_void_p]
         L.llattn_attention_host.argtypes = [c_void_p, c_void_p, POINTER(_IO), c_void_p]
         L.llattn_host_flush.argtypes = [c_void_p, c_void_p]
+        L.llattn_dense_w4a8.argtypes = [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_void_p, c_void_p]
         L.llattn_kvpool_create.argtypes = [c_int, POINTER(c_void_p)]
         L.llattn_kvpool_destroy.argtypes = [c_void_p]
         L.llattn_kvpool_destroy.restype = None
@@ -160,6 +161,18 @@ def kv_commit_paged(Kf, Vf, pool, pages, stream=None) -> None:
     if pages.numel() != nb * NKV:
         raise ValueError("pages must hold nb * 4 indices")
     _check(lib().llattn_kv_commit_paged(_ptr(Kf), _ptr(Vf), _ptr(pool), _ptr(pages), nb, _stream(stream)))
+
+
+# ------------------------------------------------------------------ consumer
+
+def dense_w4a8(W, q, s, qsum, Y, err_word=None, stream=None) -> None:
+    """Engine::gemm<4, 2>(Ly.dense, ..., oA.a, ones, HID, HID, nullptr, h, 1, 2) (engine/engine.cu:434) for any number of
+    tokens: Y [ntokens][rows] fp32 += W4.A8 projection of the int8 activations (q [ntokens][K] in fragment order, s and
+    qsum [ntokens][K/128]) with the weight strips W in the engine's device layout. Bit-identical to the reference."""
+    ntokens, K = q.shape
+    rows = Y.shape[1]
+    _check(lib().llattn_dense_w4a8(_ptr(W), _ptr(q), _ptr(s), _ptr(qsum), _ptr(Y), ntokens, rows, K,
+                                   _ptr(err_word) if err_word is not None else None, _stream(stream)))
 
 
 # ------------------------------------------------------------------ producer

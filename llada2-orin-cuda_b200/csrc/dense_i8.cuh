@@ -1,0 +1,198 @@
+// Dense W4.A8 projection with residual add on tcgen05 tensor cores (kind::i8: u8 x s8 -> s32 in tensor memory).
+//
+// It consumes the int8 activations the merge kernel writes (values in fragment order inside every 128-group, one fp32
+// scale and one int32 sum per token and group) and the reference's 4-bit weight strips as the engine holds them on the
+// device, and computes what the reference's attention-output projection computes (engine/engine.cu:434,
+// moe8::gemm<.., MODE 2>, engine/moe_i8.cu:295-400), for any number of tokens:
+//     Y[n][r] += sum over 128-groups g, in order, of  (s_w[r][g] * s_x[n][g]) * float(P[r][n][g] - z[r][g] * Sxq[n][g])
+// with P the exact integer dot product of the group. Every float operation is the reference's (one fp32 product of
+// the two scales, one fused multiply-add per group, groups in ascending order, one add into Y), so results are
+// bit-identical to the reference kernel.
+//
+// Weight strip (16 rows x K), device layout of the reference (engine/moe_i8.cu:34-41): the 1024-byte code tiles of
+// the strip's K/128 groups, then their 48-byte metas. In a code tile lane l = 4 g + t of the reference's warp owns
+// bytes 16 l .. 16 l + 15 and 512 + 16 l ..: eight words; word w (step j = w / 2, half h = w % 2) holds, for k = 32 j +
+// 16 h + 4 t + e (e = byte index), the code of row g in the low nibble and of row g + 8 in the high nibble
+// (engine/moe_i8.cu:127-160). A meta holds fp16 scale pairs (rows g | g + 8) at 4 g and zero-point pairs at 32 + 2 g.
+//
+// One CTA computes 128 weight rows x 64 tokens. Per 128-group: 128 threads unpack the eight strips' codes into a u8
+// operand tile and copy the tokens' int8 rows (both K-major, 128-byte swizzle; the weights are stored at the
+// activations' fragment positions, so the activations are copied as they are), a fifth warp issues four K = 32 MMAs
+// into one of two 64-column accumulators, and the 128 threads (thread = weight row = tensor-memory lane) fold the
+// previous group's integers into 64 fp32 accumulators while the next group's MMAs run.
+#pragma once
+#include <cuda_fp16.h>
+#include "common.cuh"
+#include "ptx.cuh"
+
+namespace llattn {
+
+constexpr int DN_ROWS = 128, DN_TOK = 64, DN_GROUP = 128;
+constexpr int DN_TILE_BYTES = 1024, DN_META_BYTES = 48;
+constexpr int DN_A_BYTES = DN_ROWS * 128, DN_B_BYTES = DN_TOK * 128;
+constexpr int DN_STAGE = DN_A_BYTES + DN_B_BYTES;                 // 24576
+// Token scales and sums are read by the folding threads themselves, and a thread may run up to three groups ahead of
+// the slowest one (it stops where it needs an MMA the slowest thread has not yet fed): four slots, not two.
+constexpr int DN_SM_SX = 2 * DN_STAGE;                            // [4][64] float token scales
+constexpr int DN_SM_SQ = DN_SM_SX + 4 * DN_TOK * 4;               // [4][64] int token sums
+constexpr int DN_SM_BAR = DN_SM_SQ + 4 * DN_TOK * 4;
+constexpr int DN_SMEM_BYTES = DN_SM_BAR + 64;
+constexpr int DN_THREADS = 160;
+enum { DB_FULL = 0, DB_DONE = 2, DB_COUNT = 4 };
+
+struct DenseParams {
+    const uint8_t* W;      // strips
+    const int8_t* q;       // [ntokens][K], fragment order inside every 128-group
+    const float* s;        // [ntokens][K / 128]
+    const int32_t* sum;    // [ntokens][K / 128]
+    float* Y;              // [ntokens][rows], accumulated into
+    int ntokens, rows, K;
+    int* err;
+};
+
+__device__ __forceinline__ void mma_i8_ss(uint32_t d, uint64_t a, uint64_t b, uint32_t idesc, uint32_t accumulate) {
+    asm volatile("{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\ttcgen05.mma.cta_group::1.kind::i8 [%0], %1, %2, %3, p;\n\t}\n"
+                 :: "r"(d), "l"(a), "l"(b), "r"(idesc), "r"(accumulate) : "memory");
+}
+// kind::i8 instruction descriptor: s32 accumulator, A u8 (format 0), B s8 (format 1), both K-major.
+__host__ __device__ constexpr uint32_t idesc_i8_u8s8(int M, int N) {
+    return (2u << 4) | (0u << 7) | (1u << 10) | (uint32_t(N >> 3) << 17) | (uint32_t(M >> 4) << 24);
+}
+
+__global__ void __launch_bounds__(DN_THREADS) dense_i8_kernel(const DenseParams p) {
+    extern __shared__ __align__(1024) uint8_t smem[];
+    __shared__ uint32_t tmem_slot;
+    __shared__ int abort_flag_s;
+    volatile int* abort_flag = &abort_flag_s;
+    const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+    const int row0 = blockIdx.x * DN_ROWS, n0 = blockIdx.y * DN_TOK;
+    const int ktot = p.K / DN_GROUP;
+    const uint32_t bar0 = ptx::smem_u32(smem + DN_SM_BAR);
+    auto BAR = [&](int i) -> uint32_t { return bar0 + 8u * uint32_t(i); };
+    if (ptx::smem_u32(smem) & 1023u) {
+        if (tid == 0 && p.err) atomicOr(p.err, ERR_SMEM_ALIGN);
+        return;
+    }
+    if (tid == 0) {
+        for (int i = 0; i < 2; ++i) { ptx::mbar_init(BAR(DB_FULL + i), 128); ptx::mbar_init(BAR(DB_DONE + i), 1); }
+        ptx::fence_mbar_init();
+        abort_flag_s = 0;
+    }
+    if (warp == 4) { ptx::tmem_alloc(ptx::smem_u32(&tmem_slot), 128); ptx::tmem_relinquish(); }
+    ptx::tc_fence_before();
+    __syncthreads();
+    ptx::tc_fence_after();
+    const uint32_t tmem = tmem_slot;
+    const size_t strip_bytes = size_t(ktot) * (DN_TILE_BYTES + DN_META_BYTES), meta_off = size_t(ktot) * DN_TILE_BYTES;
+    int errbits = 0;
+
+    if (warp < 4) {
+        // ---- this thread's weight row: strip, row inside the strip, where its scale and zero point sit in a meta
+        const int r = tid, strip = (row0 + r) >> 4, rr = r & 15, g8 = rr & 7, hi = rr >> 3;
+        const uint8_t* my_meta = p.W + size_t(strip) * strip_bytes + meta_off;
+        float c[DN_TOK];
+#pragma unroll
+        for (int n = 0; n < DN_TOK; ++n) c[n] = 0.f;
+        bool alive = true;
+#pragma unroll 1
+        for (int i = 0; i <= ktot && alive; ++i) {
+            if (i < ktot) {
+                const int st = i & 1;
+                // the stage's previous MMAs (group i - 2) have read it
+                if (i >= 2 && !ptx::mbar_wait(BAR(DB_DONE + st), ((i >> 1) - 1) & 1, abort_flag)) { alive = false; errbits |= ERR_WAIT_DEQUANT; break; }
+                uint8_t* As = smem + st * DN_STAGE;
+                uint8_t* Bs = As + DN_A_BYTES;
+                // weights: two (strip, lane) tasks per thread; each yields 8 words for row g and 8 for row g + 8
+#pragma unroll
+                for (int task = 0; task < 2; ++task) {
+                    const int id = tid + 128 * task, sl = id >> 5, l = id & 31, g = l >> 2, t = l & 3;
+                    const uint8_t* code = p.W + size_t((row0 >> 4) + sl) * strip_bytes + size_t(i) * DN_TILE_BYTES;
+                    const uint4 lo = __ldg(reinterpret_cast<const uint4*>(code) + l);
+                    const uint4 h4 = __ldg(reinterpret_cast<const uint4*>(code + 512) + l);
+                    const uint32_t w[8] = {lo.x, lo.y, lo.z, lo.w, h4.x, h4.y, h4.z, h4.w};
+                    const int ra = sl * 16 + g, rb = ra + 8;            // rows inside the CTA tile
+#pragma unroll
+                    for (int k = 0; k < 8; ++k) {
+                        const int pos = 32 * t + 8 * (k >> 1) + 4 * (k & 1);      // fragment position of the word's four codes
+                        const int chunk = pos >> 4, within = pos & 15;
+                        *reinterpret_cast<uint32_t*>(As + ra * 128 + ((chunk ^ (ra & 7)) << 4) + within) = w[k] & 0x0F0F0F0Fu;
+                        *reinterpret_cast<uint32_t*>(As + rb * 128 + ((chunk ^ (rb & 7)) << 4) + within) = (w[k] >> 4) & 0x0F0F0F0Fu;
+                    }
+                }
+                // activations: token n = tid / 2, half a 128-byte group each; tokens past the end read as zero
+                {
+                    const int n = tid >> 1, hf = tid & 1;
+                    const bool live = n0 + n < p.ntokens;
+                    const uint4* src = reinterpret_cast<const uint4*>(p.q + size_t(live ? n0 + n : 0) * p.K + size_t(i) * DN_GROUP) + 4 * hf;
+#pragma unroll
+                    for (int k = 0; k < 4; ++k) {
+                        const uint4 v = live ? __ldg(src + k) : make_uint4(0, 0, 0, 0);
+                        *reinterpret_cast<uint4*>(Bs + n * 128 + (((4 * hf + k) ^ (n & 7)) << 4)) = v;
+                    }
+                    if (tid < DN_TOK) {
+                        const bool lv = n0 + tid < p.ntokens;
+                        reinterpret_cast<float*>(smem + DN_SM_SX)[(i & 3) * DN_TOK + tid] = lv ? p.s[size_t(n0 + tid) * ktot + i] : 0.f;
+                        reinterpret_cast<int*>(smem + DN_SM_SQ)[(i & 3) * DN_TOK + tid] = lv ? p.sum[size_t(n0 + tid) * ktot + i] : 0;
+                    }
+                }
+                ptx::fence_proxy_async_smem();
+                ptx::mbar_arrive(BAR(DB_FULL + st));
+            }
+            if (i >= 1) {
+                // ---- fold group i - 1: its integers are complete in accumulator (i - 1) % 2
+                const int gi = i - 1, st = gi & 1;
+                if (!ptx::mbar_wait(BAR(DB_DONE + st), (gi >> 1) & 1, abort_flag)) { alive = false; errbits |= ERR_WAIT_DEQUANT; break; }
+                ptx::tc_fence_after();
+                const uint8_t* m = my_meta + size_t(gi) * DN_META_BYTES;
+                const float sw = __half2float(__ushort_as_half(*reinterpret_cast<const uint16_t*>(m + 4 * g8 + 2 * hi)));
+                const int z = int(m[32 + 2 * g8 + hi]);
+                const float* sx = reinterpret_cast<const float*>(smem + DN_SM_SX) + (gi & 3) * DN_TOK;
+                const int* sq = reinterpret_cast<const int*>(smem + DN_SM_SQ) + (gi & 3) * DN_TOK;
+#pragma unroll
+                for (int h = 0; h < 2; ++h) {
+                    uint32_t d[32];
+                    ptx::tmem_ld32(tmem + (uint32_t(warp * 32) << 16) + st * DN_TOK + 32 * h, d);
+                    ptx::tmem_wait_ld();
+#pragma unroll
+                    for (int n = 0; n < 32; ++n) {
+                        const int v = int(d[n]) - z * sq[32 * h + n];
+                        c[32 * h + n] = __fmaf_rn(__fmul_rn(sw, sx[32 * h + n]), __int2float_rn(v), c[32 * h + n]);
+                    }
+                }
+                ptx::tc_fence_before();
+            }
+        }
+        if (alive) {
+#pragma unroll
+            for (int n = 0; n < DN_TOK; ++n)
+                if (n0 + n < p.ntokens) {
+                    float* o = p.Y + size_t(n0 + n) * p.rows + row0 + r;
+                    *o = *o + c[n];
+                }
+        }
+    } else {
+        // ---- MMA issue: group i = four K-steps of 32 into accumulator i % 2, overwriting it
+        const uint32_t id = idesc_i8_u8s8(DN_ROWS, DN_TOK);
+        bool alive = true;
+#pragma unroll 1
+        for (int i = 0; i < ktot && alive; ++i) {
+            const int st = i & 1;
+            if (!ptx::mbar_wait(BAR(DB_FULL + st), (i >> 1) & 1, abort_flag)) { alive = false; errbits |= ERR_WAIT_MMA; break; }
+            ptx::tc_fence_after();
+            if (ptx::elect_one()) {
+                const uint32_t a_s = ptx::smem_u32(smem + st * DN_STAGE), b_s = a_s + DN_A_BYTES;
+#pragma unroll
+                for (int k = 0; k < 4; ++k)
+                    mma_i8_ss(tmem + st * DN_TOK, ptx::smem_desc_sw128(a_s + 32 * k, 16, 1024), ptx::smem_desc_sw128(b_s + 32 * k, 16, 1024), id, k > 0);
+                ptx::mma_commit(BAR(DB_DONE + st));
+            }
+            __syncwarp();
+        }
+    }
+    if (errbits && p.err) atomicOr(p.err, errbits);
+    ptx::tc_fence_before();
+    __syncthreads();
+    if (warp == 4) ptx::tmem_dealloc(tmem, 128);
+}
+
+}  // namespace llattn

@@ -16,6 +16,7 @@
 #include "attn_kernel.cuh"
 #include "merge_kernel.cuh"
 #include "qk_norm_rope.cuh"
+#include "dense_i8.cuh"
 
 namespace {
 
@@ -154,6 +155,30 @@ int llattn_qk_norm_rope(const float* qkv, const int32_t* pos, const float* gq, c
     if (T == 0) return LLATTN_OK;
     llattn::qk_norm_rope_kernel<<<dim3(T, 3), llattn::ROPE_THREADS, 0, as_stream(stream)>>>(
         qkv, pos, gq, gk, eps, inv_freq, static_cast<half*>(q), static_cast<half*>(k), static_cast<half*>(v));
+    CU(cudaGetLastError());
+    return LLATTN_OK;
+}
+
+// ------------------------------------------------------------------------------------------------------ consumer
+// The attention-output projection on the int8 activations the merge kernel writes.
+
+int llattn_dense_w4a8(const void* W, const int8_t* q, const float* s, const int32_t* sum, float* Y, int ntokens, int rows, int K,
+                      int* err_word, void* stream) {
+    if (!W || !q || !s || !sum || !Y) return fail(LLATTN_EINVAL, "dense_w4a8: null pointer");
+    if (ntokens < 0 || ntokens > 1 << 22) return fail(LLATTN_EINVAL, "dense_w4a8: ntokens = %d", ntokens);
+    if (rows <= 0 || rows % llattn::DN_ROWS || K <= 0 || K % llattn::DN_GROUP || K > 1 << 20 || rows > 1 << 20)
+        return fail(LLATTN_EINVAL, "dense_w4a8: rows = %d, K = %d (both multiples of 128)", rows, K);
+    if (ntokens == 0) return LLATTN_OK;
+    static std::once_flag once[64];
+    int dev = 0;
+    CU(cudaGetDevice(&dev));
+    if (dev >= 0 && dev < 64)
+        std::call_once(once[dev], [] {
+            cudaFuncSetAttribute(llattn::dense_i8_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, llattn::DN_SMEM_BYTES);
+        });
+    llattn::DenseParams p{static_cast<const uint8_t*>(W), q, s, sum, Y, ntokens, rows, K, err_word};
+    const dim3 grid(rows / llattn::DN_ROWS, (ntokens + llattn::DN_TOK - 1) / llattn::DN_TOK);
+    llattn::dense_i8_kernel<<<grid, llattn::DN_THREADS, llattn::DN_SMEM_BYTES, as_stream(stream)>>>(p);
     CU(cudaGetLastError());
     return LLATTN_OK;
 }

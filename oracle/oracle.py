@@ -55,6 +55,8 @@ def lib() -> ctypes.CDLL:
         L.orc_h2f.restype = ctypes.c_float
         L.orc_num_threads.restype = i32
         L.orc_qk_norm_rope.argtypes = [vp, vp, vp, vp, ctypes.c_float, vp, vp, vp, vp, i32]
+        L.orc_dense_w4a8.argtypes = [vp, vp, vp, vp, vp, i32, i32, i32]
+        L.orc_dense_w4a8.restype = None
     return _lib
 
 
@@ -127,6 +129,17 @@ def qk_norm_rope(qkv, pos, gq, gk, eps, inv_freq):
                            _p(np.ascontiguousarray(gq, np.float32)), _p(np.ascontiguousarray(gk, np.float32)), float(eps),
                            _p(np.ascontiguousarray(inv_freq, np.float32)), _p(q), _p(k), _p(v), T)
     return q, k, v
+
+
+def dense_w4a8(W: np.ndarray, q: np.ndarray, s: np.ndarray, qsum: np.ndarray, Y: np.ndarray) -> None:
+    """Y [ntokens][rows] float32 += the W4.A8 projection (engine/moe_i8.cu:295-400, MODE 2). W: uint8 strips in the
+    engine's device layout [rows/16][K/128 * 1024 + K/128 * 48]; q int8 [ntokens][K] in fragment order; s float32 and
+    qsum int32 [ntokens][K/128]."""
+    ntokens, K = q.shape
+    rows = Y.shape[1]
+    assert W.dtype == np.uint8 and W.size == rows // 16 * (K // 128) * 1072 and Y.dtype == np.float32
+    lib().orc_dense_w4a8(_p(W), _p(q), _p(np.ascontiguousarray(s, np.float32)), _p(np.ascontiguousarray(qsum, np.int32)), _p(Y),
+                         ntokens, rows, K)
 
 
 def frag_pos(c: int) -> int:

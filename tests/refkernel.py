@@ -79,3 +79,35 @@ def qk_norm_rope(qkv, pos, gq, gk, eps, inv_freq, q, k, v):
     rc = _ops.ref_qk_norm_rope(qkv.data_ptr(), pos.data_ptr(), gq.data_ptr(), gk.data_ptr(), eps, inv_freq.data_ptr(),
                                q.data_ptr(), k.data_ptr(), v.data_ptr(), qkv.shape[0], torch.cuda.current_stream().cuda_stream)
     assert rc == 0, rc
+
+
+GEMM_PATH = os.path.join(ROOT, "oracle", "_ref", "libgemm_ref.so")
+_gemm = None
+
+
+def gemm_available() -> bool:
+    return os.path.exists(GEMM_PATH)
+
+
+def dense_w4a8(W, q, s, qsum, Y):
+    """The reference's own moe8::gemm<4, 4, 2, 2> (engine/moe_i8.cu:408), launched as the engine launches its attention
+    output projection (engine/engine.cu:434): Y += projection, tokens in work items of 32."""
+    import numpy as np
+    import torch
+    global _gemm
+    if _gemm is None:
+        _gemm = ctypes.CDLL(GEMM_PATH)
+        vp, i = ctypes.c_void_p, ctypes.c_int
+        _gemm.ref_dense_w4a8.argtypes = [vp, vp, vp, vp, vp, i, i, i, vp, vp, vp, vp, i, vp]
+    ntokens, K = q.shape
+    rows = Y.shape[1]
+    dev = q.device
+    work = torch.from_numpy(np.array([[0, 32 * j, 32] for j in range(ntokens // 32)], np.int32)).to(dev)
+    off = torch.zeros(1, dtype=torch.int64, device=dev)
+    bits = torch.full((1,), 4, dtype=torch.int8, device=dev)
+    ones = torch.ones(ntokens, dtype=torch.float32, device=dev)
+    rc = _gemm.ref_dense_w4a8(W.data_ptr(), q.data_ptr(), s.data_ptr(), qsum.data_ptr(), Y.data_ptr(), ntokens, rows, K,
+                              work.data_ptr(), off.data_ptr(), bits.data_ptr(), ones.data_ptr(), 2,
+                              torch.cuda.current_stream().cuda_stream)
+    assert rc == 0, rc
+    torch.cuda.synchronize()
