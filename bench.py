@@ -55,6 +55,8 @@ def parse():
     ap.add_argument("--no-graph", action="store_true")
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-e2e", action="store_true")
+    ap.add_argument("--dense", action="store_true",
+                    help="time the W4.A8 attention-output projection (the consumer of the path) instead; own JSON line")
     return ap.parse_args()
 
 
@@ -403,6 +405,61 @@ def run_ours(a):
         dist.destroy_process_group()
 
 
+def run_dense(a):
+    """Side measurement, not the contract line: the 2048 x 2048 W4.A8 projection that consumes the attention output, on
+    the tokens of one step (--nseq x 32), device-resident inputs, CUDA events, a buffer larger than L2 written between
+    launches. Also times the reference's own GEMM when its library travelled (oracle/_ref/libgemm_ref.so)."""
+    import numpy as np
+    import torch
+    api = importlib.import_module(PKG + ".api")
+    wl = importlib.import_module(PKG).workload
+    torch.cuda.set_device(0)
+    dev = torch.device("cuda:0")
+    rows = K = 2048
+    ntok = a.nseq * 32
+    strips, _, _, _ = wl.dense_weights(rows, K, 1)
+    q, s, qsum = wl.int8_activations(ntok, K, 2)
+    d = [torch.from_numpy(x).to(dev) for x in (strips, q, s, qsum)]
+    Y = torch.zeros((ntok, rows), dtype=torch.float32, device=dev)
+    flush = torch.empty(256 << 20, dtype=torch.uint8, device=dev)
+    err = torch.zeros(1, dtype=torch.int32, device=dev)
+
+    def timed(fn):
+        for _ in range(max(a.warmup, 3)):
+            fn()
+        ts = []
+        for _ in range(a.steps):
+            flush.fill_(1)
+            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            e0.record(); fn(); e1.record()
+            torch.cuda.synchronize()
+            ts.append(e0.elapsed_time(e1))
+        return statistics.median(ts)
+
+    ms = timed(lambda: api.dense_w4a8(d[0], d[1], d[2], d[3], Y, err_word=err))
+    assert int(err.item()) == 0
+    pk = peaks()
+    ktot = K // 128
+    bytes_alg = strips.size + ntok * K + 2 * 4 * ntok * ktot + 2 * 4 * ntok * rows      # weights, int8 acts, scales+sums, Y read+write
+    ops = 2.0 * ntok * rows * K
+    out = {"metric": "W4.A8 attention-output projection tokens/s", "value": ntok / (ms * 1e-3), "unit": "tok/s", "n_gpus": 1,
+           "steps": a.steps, "warmup": max(a.warmup, 3), "ms_per_step": ms, "higher_is_better": True, "dtype": "u8 x s8 -> s32, fp32 scale chain",
+           "data": "synthetic", "config": {"workload": f"{ntok} tokens x (2048 x 2048, 4-bit weights, int8 activations), Y += W x", "l2": "256 MB written between launches"},
+           "roofline": {"bound": "hbm", "achieved": bytes_alg / (ms * 1e-3) / 1e9, "peak": pk["hbm"], "unit": "GB/s",
+                        "frac": bytes_alg / (ms * 1e-3) / 1e9 / pk["hbm"], "traffic": None, "algorithmic_bytes": bytes_alg,
+                        "int8_tops": ops / (ms * 1e-3) / 1e12, "peak_source": pk["src"]},
+           "gpu_launches": a.steps}
+    sys.path.insert(0, os.path.join(ROOT, "tests"))
+    try:
+        import refkernel
+        if refkernel.gemm_available() and ntok % 32 == 0:
+            aux = refkernel.dense_aux(ntok, dev)
+            out["reference_kernel_ms"] = timed(lambda: refkernel.dense_w4a8(d[0], d[1], d[2], d[3], Y, aux=aux, sync=False))
+    except Exception as e:  # noqa: BLE001
+        out["reference_kernel_ms"] = f"unavailable: {e}"
+    print(json.dumps(out))
+
+
 if __name__ == "__main__":
     # Libraries (NCCL's version banner, torchrun notices) may write to stdout; the contract is ONE JSON line there. Everything
     # written to fd 1 from here on goes to stderr, and the JSON line is written to the saved stdout.
@@ -417,7 +474,9 @@ if __name__ == "__main__":
         _real_stdout.flush()
 
     args = parse()
-    if args.impl == "reference":
+    if args.dense:
+        run_dense(args)
+    elif args.impl == "reference":
         run_reference(args)
     else:
         run_ours(args)

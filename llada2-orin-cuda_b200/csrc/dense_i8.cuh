@@ -29,13 +29,16 @@ namespace llattn {
 
 constexpr int DN_ROWS = 128, DN_TOK = 64, DN_GROUP = 128;
 constexpr int DN_TILE_BYTES = 1024, DN_META_BYTES = 48;
-constexpr int DN_A_BYTES = DN_ROWS * 128, DN_B_BYTES = DN_TOK * 128;
-constexpr int DN_STAGE = DN_A_BYTES + DN_B_BYTES;                 // 24576
-// Token scales and sums are read by the folding threads themselves, and a thread may run up to three groups ahead of
-// the slowest one (it stops where it needs an MMA the slowest thread has not yet fed): four slots, not two.
-constexpr int DN_SM_SX = 2 * DN_STAGE;                            // [4][64] float token scales
-constexpr int DN_SM_SQ = DN_SM_SX + 4 * DN_TOK * 4;               // [4][64] int token sums
-constexpr int DN_SM_BAR = DN_SM_SQ + 4 * DN_TOK * 4;
+constexpr int DN_STAGES = 4;                                      // groups in flight from global memory
+constexpr int DN_A_BYTES = DN_ROWS * 128, DN_B_BYTES = DN_TOK * 128, DN_RAW_BYTES = 8 * DN_TILE_BYTES;
+constexpr int DN_SM_A = 0;                                        // two unpacked weight tiles
+constexpr int DN_SM_B = DN_SM_A + 2 * DN_A_BYTES;                 // DN_STAGES activation tiles, written by cp.async
+constexpr int DN_SM_RAW = DN_SM_B + DN_STAGES * DN_B_BYTES;       // DN_STAGES x eight code tiles as they lie in memory
+// Token scales and sums are read by the folding threads themselves; a thread may be one group ahead of the slowest one
+// when it refills a slot, so these have twice as many slots as there are stages.
+constexpr int DN_SM_SX = DN_SM_RAW + DN_STAGES * DN_RAW_BYTES;    // [8][64] float token scales
+constexpr int DN_SM_SQ = DN_SM_SX + 8 * DN_TOK * 4;               // [8][64] int token sums
+constexpr int DN_SM_BAR = DN_SM_SQ + 8 * DN_TOK * 4;
 constexpr int DN_SMEM_BYTES = DN_SM_BAR + 64;
 constexpr int DN_THREADS = 160;
 enum { DB_FULL = 0, DB_DONE = 2, DB_COUNT = 4 };
@@ -54,6 +57,16 @@ __device__ __forceinline__ void mma_i8_ss(uint32_t d, uint64_t a, uint64_t b, ui
     asm volatile("{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\ttcgen05.mma.cta_group::1.kind::i8 [%0], %1, %2, %3, p;\n\t}\n"
                  :: "r"(d), "l"(a), "l"(b), "r"(idesc), "r"(accumulate) : "memory");
 }
+// 16-byte and 4-byte asynchronous copies global -> shared (per-thread completion groups); `live` false writes zeros.
+__device__ __forceinline__ void cp_async16(uint32_t dst, const void* src, bool live) {
+    asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;" ::"r"(dst), "l"(src), "r"(live ? 16 : 0) : "memory");
+}
+__device__ __forceinline__ void cp_async4(uint32_t dst, const void* src, bool live) {
+    asm volatile("cp.async.ca.shared.global [%0], [%1], 4, %2;" ::"r"(dst), "l"(src), "r"(live ? 4 : 0) : "memory");
+}
+__device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;" ::: "memory"); }
+template <int kPending> __device__ __forceinline__ void cp_async_wait() { asm volatile("cp.async.wait_group %0;" ::"n"(kPending) : "memory"); }
+
 // kind::i8 instruction descriptor: s32 accumulator, A u8 (format 0), B s8 (format 1), both K-major.
 __host__ __device__ constexpr uint32_t idesc_i8_u8s8(int M, int N) {
     return (2u << 4) | (0u << 7) | (1u << 10) | (uint32_t(N >> 3) << 17) | (uint32_t(M >> 4) << 24);
@@ -89,65 +102,91 @@ __global__ void __launch_bounds__(DN_THREADS) dense_i8_kernel(const DenseParams 
     if (warp < 4) {
         // ---- this thread's weight row: strip, row inside the strip, where its scale and zero point sit in a meta
         const int r = tid, strip = (row0 + r) >> 4, rr = r & 15, g8 = rr & 7, hi = rr >> 3;
-        const uint8_t* my_meta = p.W + size_t(strip) * strip_bytes + meta_off;
+        const uint8_t* my_meta = p.W + size_t(strip) * strip_bytes + meta_off + 4 * g8 + 2 * hi;
+        const uint8_t* my_zero = p.W + size_t(strip) * strip_bytes + meta_off + 32 + 2 * g8 + hi;
+        // what this thread brings in and stages per group: two (strip, reference lane) tasks of weight codes - it unpacks
+        // exactly the bytes it copied itself - and half a token's 128-byte row, copied straight into the operand tile
+        const int sl0 = tid >> 5, l = tid & 31, g = l >> 2, t = l & 3;       // task 0: strip sl0, task 1: strip sl0 + 4
+        const uint8_t* code0 = p.W + size_t((row0 >> 4) + sl0) * strip_bytes + 16 * l;
+        const uint8_t* code1 = code0 + 4 * strip_bytes;
+        const int tn = tid >> 1, hf = tid & 1;
+        const bool tlive = n0 + tn < p.ntokens;
+        const int8_t* arow = p.q + size_t(tlive ? n0 + tn : 0) * p.K + 64 * hf;
+        const bool slive = tid < DN_TOK && n0 + tid < p.ntokens;
+        const size_t srow = size_t(slive ? n0 + tid : 0) * ktot;
+        const uint32_t sm0 = ptx::smem_u32(smem);
+        const uint32_t raw_mine = sm0 + DN_SM_RAW + 64 * tid;             // 4 x 16 bytes per stage
+        const uint32_t b_mine = sm0 + DN_SM_B + tn * 128;
+        auto fetch = [&](int i) {          // asynchronous copies of group i (always one commit, so groups count uniformly)
+            if (i < ktot) {
+                const int sg = i & (DN_STAGES - 1);
+                const size_t co = size_t(i) * DN_TILE_BYTES;
+                cp_async16(raw_mine + sg * DN_RAW_BYTES, code0 + co, true);
+                cp_async16(raw_mine + sg * DN_RAW_BYTES + 16, code0 + co + 512, true);
+                cp_async16(raw_mine + sg * DN_RAW_BYTES + 32, code1 + co, true);
+                cp_async16(raw_mine + sg * DN_RAW_BYTES + 48, code1 + co + 512, true);
+                const int8_t* src = arow + size_t(i) * DN_GROUP;
+#pragma unroll
+                for (int k = 0; k < 4; ++k)
+                    cp_async16(b_mine + sg * DN_B_BYTES + (((4 * hf + k) ^ (tn & 7)) << 4), src + 16 * k, tlive);
+                if (tid < DN_TOK) {
+                    cp_async4(sm0 + DN_SM_SX + ((i & 7) * DN_TOK + tid) * 4, p.s + srow + i, slive);
+                    cp_async4(sm0 + DN_SM_SQ + ((i & 7) * DN_TOK + tid) * 4, p.sum + srow + i, slive);
+                }
+            }
+            cp_async_commit();
+        };
         float c[DN_TOK];
 #pragma unroll
         for (int n = 0; n < DN_TOK; ++n) c[n] = 0.f;
         bool alive = true;
+        uint16_t sw_next = 0;
+        int z_next = 0;
+#pragma unroll
+        for (int i = 0; i < DN_STAGES - 1; ++i) fetch(i);
 #pragma unroll 1
         for (int i = 0; i <= ktot && alive; ++i) {
+            // scale and zero point of the group folded in this iteration (loaded one iteration ago, behind the proxy fence:
+            // a fence with loads in flight waits for them)
+            const uint16_t sw_bits = sw_next;
+            const int z = z_next;
             if (i < ktot) {
                 const int st = i & 1;
-                // the stage's previous MMAs (group i - 2) have read it
-                if (i >= 2 && !ptx::mbar_wait(BAR(DB_DONE + st), ((i >> 1) - 1) & 1, abort_flag)) { alive = false; errbits |= ERR_WAIT_DEQUANT; break; }
-                uint8_t* As = smem + st * DN_STAGE;
-                uint8_t* Bs = As + DN_A_BYTES;
-                // weights: two (strip, lane) tasks per thread; each yields 8 words for row g and 8 for row g + 8
+                // group i has landed (this thread's copies; the two younger groups may still be in flight). The A tile's
+                // previous MMAs (group i - 2) were seen complete when this thread folded that group.
+                cp_async_wait<DN_STAGES - 2>();
+                uint8_t* As = smem + DN_SM_A + st * DN_A_BYTES;
+                const uint4* raw = reinterpret_cast<const uint4*>(smem + DN_SM_RAW + (i & (DN_STAGES - 1)) * DN_RAW_BYTES + 64 * tid);
+                // weights: each task yields 8 words for row g of its strip and 8 for row g + 8, stored at the codes'
+                // fragment positions
 #pragma unroll
                 for (int task = 0; task < 2; ++task) {
-                    const int id = tid + 128 * task, sl = id >> 5, l = id & 31, g = l >> 2, t = l & 3;
-                    const uint8_t* code = p.W + size_t((row0 >> 4) + sl) * strip_bytes + size_t(i) * DN_TILE_BYTES;
-                    const uint4 lo = __ldg(reinterpret_cast<const uint4*>(code) + l);
-                    const uint4 h4 = __ldg(reinterpret_cast<const uint4*>(code + 512) + l);
+                    const uint4 lo = raw[2 * task], h4 = raw[2 * task + 1];
                     const uint32_t w[8] = {lo.x, lo.y, lo.z, lo.w, h4.x, h4.y, h4.z, h4.w};
-                    const int ra = sl * 16 + g, rb = ra + 8;            // rows inside the CTA tile
+                    const int ra = (sl0 + 4 * task) * 16 + g, rb = ra + 8;            // rows inside the CTA tile
 #pragma unroll
                     for (int k = 0; k < 8; ++k) {
-                        const int pos = 32 * t + 8 * (k >> 1) + 4 * (k & 1);      // fragment position of the word's four codes
+                        const int pos = 32 * t + 8 * (k >> 1) + 4 * (k & 1);
                         const int chunk = pos >> 4, within = pos & 15;
                         *reinterpret_cast<uint32_t*>(As + ra * 128 + ((chunk ^ (ra & 7)) << 4) + within) = w[k] & 0x0F0F0F0Fu;
                         *reinterpret_cast<uint32_t*>(As + rb * 128 + ((chunk ^ (rb & 7)) << 4) + within) = (w[k] >> 4) & 0x0F0F0F0Fu;
                     }
                 }
-                // activations: token n = tid / 2, half a 128-byte group each; tokens past the end read as zero
-                {
-                    const int n = tid >> 1, hf = tid & 1;
-                    const bool live = n0 + n < p.ntokens;
-                    const uint4* src = reinterpret_cast<const uint4*>(p.q + size_t(live ? n0 + n : 0) * p.K + size_t(i) * DN_GROUP) + 4 * hf;
-#pragma unroll
-                    for (int k = 0; k < 4; ++k) {
-                        const uint4 v = live ? __ldg(src + k) : make_uint4(0, 0, 0, 0);
-                        *reinterpret_cast<uint4*>(Bs + n * 128 + (((4 * hf + k) ^ (n & 7)) << 4)) = v;
-                    }
-                    if (tid < DN_TOK) {
-                        const bool lv = n0 + tid < p.ntokens;
-                        reinterpret_cast<float*>(smem + DN_SM_SX)[(i & 3) * DN_TOK + tid] = lv ? p.s[size_t(n0 + tid) * ktot + i] : 0.f;
-                        reinterpret_cast<int*>(smem + DN_SM_SQ)[(i & 3) * DN_TOK + tid] = lv ? p.sum[size_t(n0 + tid) * ktot + i] : 0;
-                    }
-                }
-                ptx::fence_proxy_async_smem();
+                ptx::fence_proxy_async_smem();         // the A tile, and the activation tile the copies wrote, for the tensor core
                 ptx::mbar_arrive(BAR(DB_FULL + st));
+                sw_next = __ldg(reinterpret_cast<const uint16_t*>(my_meta + size_t(i) * DN_META_BYTES));
+                z_next = int(__ldg(my_zero + size_t(i) * DN_META_BYTES));
             }
             if (i >= 1) {
-                // ---- fold group i - 1: its integers are complete in accumulator (i - 1) % 2
+                // ---- fold group i - 1: its integers are complete in accumulator (i - 1) % 2. The token scales were
+                // written by other threads' copies: their arrivals on db_full order them before this read.
                 const int gi = i - 1, st = gi & 1;
+                if (!ptx::mbar_wait(BAR(DB_FULL + st), (gi >> 1) & 1, abort_flag)) { alive = false; errbits |= ERR_WAIT_DEQUANT; break; }
                 if (!ptx::mbar_wait(BAR(DB_DONE + st), (gi >> 1) & 1, abort_flag)) { alive = false; errbits |= ERR_WAIT_DEQUANT; break; }
                 ptx::tc_fence_after();
-                const uint8_t* m = my_meta + size_t(gi) * DN_META_BYTES;
-                const float sw = __half2float(__ushort_as_half(*reinterpret_cast<const uint16_t*>(m + 4 * g8 + 2 * hi)));
-                const int z = int(m[32 + 2 * g8 + hi]);
-                const float* sx = reinterpret_cast<const float*>(smem + DN_SM_SX) + (gi & 3) * DN_TOK;
-                const int* sq = reinterpret_cast<const int*>(smem + DN_SM_SQ) + (gi & 3) * DN_TOK;
+                const float sw = __half2float(__ushort_as_half(sw_bits));
+                const float* sx = reinterpret_cast<const float*>(smem + DN_SM_SX) + (gi & 7) * DN_TOK;
+                const int* sq = reinterpret_cast<const int*>(smem + DN_SM_SQ) + (gi & 7) * DN_TOK;
 #pragma unroll
                 for (int h = 0; h < 2; ++h) {
                     uint32_t d[32];
@@ -155,20 +194,32 @@ __global__ void __launch_bounds__(DN_THREADS) dense_i8_kernel(const DenseParams 
                     ptx::tmem_wait_ld();
 #pragma unroll
                     for (int n = 0; n < 32; ++n) {
+                        // int -> float through the float whose bits are 1.5 * 2^23 + v: exact for |v| < 2^22 (here
+                        // |v| <= 255 * 127 * 128), one integer add and one float subtract at full rate
                         const int v = int(d[n]) - z * sq[32 * h + n];
-                        c[32 * h + n] = __fmaf_rn(__fmul_rn(sw, sx[32 * h + n]), __int2float_rn(v), c[32 * h + n]);
+                        const float vf = __int_as_float(v + 0x4B400000) - 12582912.0f;
+                        c[32 * h + n] = __fmaf_rn(__fmul_rn(sw, sx[32 * h + n]), vf, c[32 * h + n]);
                     }
                 }
                 ptx::tc_fence_before();
             }
+            // the slots of group i - 1 (activation tile read by its MMAs, now complete) take group i + 3
+            fetch(i + DN_STAGES - 1);
         }
+        cp_async_wait<0>();
         if (alive) {
+            // Y += c, sixteen tokens at a time: all loads of a batch are issued before the first add, so the round trips
+            // to memory overlap instead of queueing behind one another (one coalesced 128-byte line per warp and token)
+            float* ybase = p.Y + size_t(n0) * p.rows + row0 + r;
 #pragma unroll
-            for (int n = 0; n < DN_TOK; ++n)
-                if (n0 + n < p.ntokens) {
-                    float* o = p.Y + size_t(n0 + n) * p.rows + row0 + r;
-                    *o = *o + c[n];
-                }
+            for (int nb = 0; nb < DN_TOK; nb += 16) {
+                float y[16];
+#pragma unroll
+                for (int j = 0; j < 16; ++j) y[j] = n0 + nb + j < p.ntokens ? __ldcg(ybase + size_t(nb + j) * p.rows) : 0.f;
+#pragma unroll
+                for (int j = 0; j < 16; ++j)
+                    if (n0 + nb + j < p.ntokens) __stcg(ybase + size_t(nb + j) * p.rows, y[j] + c[nb + j]);
+            }
         }
     } else {
         // ---- MMA issue: group i = four K-steps of 32 into accumulator i % 2, overwriting it
@@ -180,7 +231,8 @@ __global__ void __launch_bounds__(DN_THREADS) dense_i8_kernel(const DenseParams 
             if (!ptx::mbar_wait(BAR(DB_FULL + st), (i >> 1) & 1, abort_flag)) { alive = false; errbits |= ERR_WAIT_MMA; break; }
             ptx::tc_fence_after();
             if (ptx::elect_one()) {
-                const uint32_t a_s = ptx::smem_u32(smem + st * DN_STAGE), b_s = a_s + DN_A_BYTES;
+                const uint32_t a_s = ptx::smem_u32(smem + DN_SM_A + st * DN_A_BYTES);
+                const uint32_t b_s = ptx::smem_u32(smem + DN_SM_B + (i & (DN_STAGES - 1)) * DN_B_BYTES);
 #pragma unroll
                 for (int k = 0; k < 4; ++k)
                     mma_i8_ss(tmem + st * DN_TOK, ptx::smem_desc_sw128(a_s + 32 * k, 16, 1024), ptx::smem_desc_sw128(b_s + 32 * k, 16, 1024), id, k > 0);

@@ -89,10 +89,18 @@ def gemm_available() -> bool:
     return os.path.exists(GEMM_PATH)
 
 
-def dense_w4a8(W, q, s, qsum, Y):
+def dense_aux(ntokens, dev):
+    """Work items of 32 tokens, a one-entry expert table and unit slot weights for dense_w4a8 (device tensors)."""
+    import numpy as np
+    import torch
+    work = torch.from_numpy(np.array([[0, 32 * j, 32] for j in range(ntokens // 32)], np.int32)).to(dev)
+    return (work, torch.zeros(1, dtype=torch.int64, device=dev), torch.full((1,), 4, dtype=torch.int8, device=dev),
+            torch.ones(ntokens, dtype=torch.float32, device=dev))
+
+
+def dense_w4a8(W, q, s, qsum, Y, aux=None, sync=True):
     """The reference's own moe8::gemm<4, 4, 2, 2> (engine/moe_i8.cu:408), launched as the engine launches its attention
     output projection (engine/engine.cu:434): Y += projection, tokens in work items of 32."""
-    import numpy as np
     import torch
     global _gemm
     if _gemm is None:
@@ -101,13 +109,10 @@ def dense_w4a8(W, q, s, qsum, Y):
         _gemm.ref_dense_w4a8.argtypes = [vp, vp, vp, vp, vp, i, i, i, vp, vp, vp, vp, i, vp]
     ntokens, K = q.shape
     rows = Y.shape[1]
-    dev = q.device
-    work = torch.from_numpy(np.array([[0, 32 * j, 32] for j in range(ntokens // 32)], np.int32)).to(dev)
-    off = torch.zeros(1, dtype=torch.int64, device=dev)
-    bits = torch.full((1,), 4, dtype=torch.int8, device=dev)
-    ones = torch.ones(ntokens, dtype=torch.float32, device=dev)
+    work, off, bits, ones = aux if aux is not None else dense_aux(ntokens, q.device)
     rc = _gemm.ref_dense_w4a8(W.data_ptr(), q.data_ptr(), s.data_ptr(), qsum.data_ptr(), Y.data_ptr(), ntokens, rows, K,
                               work.data_ptr(), off.data_ptr(), bits.data_ptr(), ones.data_ptr(), 2,
                               torch.cuda.current_stream().cuda_stream)
     assert rc == 0, rc
-    torch.cuda.synchronize()
+    if sync:
+        torch.cuda.synchronize()
