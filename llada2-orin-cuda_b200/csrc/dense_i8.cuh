@@ -29,14 +29,15 @@ namespace llattn {
 
 constexpr int DN_ROWS = 128, DN_TOK = 64, DN_GROUP = 128;
 constexpr int DN_TILE_BYTES = 1024, DN_META_BYTES = 48;
-constexpr int DN_STAGES = 4;                                      // groups in flight from global memory
+constexpr int DN_STAGES = 3;                                      // slots for data coming from global memory
 constexpr int DN_A_BYTES = DN_ROWS * 128, DN_B_BYTES = DN_TOK * 128, DN_RAW_BYTES = 8 * DN_TILE_BYTES;
 constexpr int DN_SM_A = 0;                                        // two unpacked weight tiles
 constexpr int DN_SM_B = DN_SM_A + 2 * DN_A_BYTES;                 // DN_STAGES activation tiles, written by cp.async
-constexpr int DN_SM_RAW = DN_SM_B + DN_STAGES * DN_B_BYTES;       // DN_STAGES x eight code tiles as they lie in memory
+constexpr int DN_SM_RAW = DN_SM_B + DN_STAGES * DN_B_BYTES;       // eight code tiles as they lie in memory (every thread copies and
+                                                                  // unpacks its own 64 bytes, so one slot is enough)
 // Token scales and sums are read by the folding threads themselves; a thread may be one group ahead of the slowest one
 // when it refills a slot, so these have twice as many slots as there are stages.
-constexpr int DN_SM_SX = DN_SM_RAW + DN_STAGES * DN_RAW_BYTES;    // [8][64] float token scales
+constexpr int DN_SM_SX = DN_SM_RAW + DN_RAW_BYTES;                // [8][64] float token scales
 constexpr int DN_SM_SQ = DN_SM_SX + 8 * DN_TOK * 4;               // [8][64] int token sums
 constexpr int DN_SM_BAR = DN_SM_SQ + 8 * DN_TOK * 4;
 constexpr int DN_SMEM_BYTES = DN_SM_BAR + 64;
@@ -119,12 +120,12 @@ __global__ void __launch_bounds__(DN_THREADS) dense_i8_kernel(const DenseParams 
         const uint32_t b_mine = sm0 + DN_SM_B + tn * 128;
         auto fetch = [&](int i) {          // asynchronous copies of group i (always one commit, so groups count uniformly)
             if (i < ktot) {
-                const int sg = i & (DN_STAGES - 1);
+                const int sg = i % DN_STAGES;
                 const size_t co = size_t(i) * DN_TILE_BYTES;
-                cp_async16(raw_mine + sg * DN_RAW_BYTES, code0 + co, true);
-                cp_async16(raw_mine + sg * DN_RAW_BYTES + 16, code0 + co + 512, true);
-                cp_async16(raw_mine + sg * DN_RAW_BYTES + 32, code1 + co, true);
-                cp_async16(raw_mine + sg * DN_RAW_BYTES + 48, code1 + co + 512, true);
+                cp_async16(raw_mine, code0 + co, true);
+                cp_async16(raw_mine + 16, code0 + co + 512, true);
+                cp_async16(raw_mine + 32, code1 + co, true);
+                cp_async16(raw_mine + 48, code1 + co + 512, true);
                 const int8_t* src = arow + size_t(i) * DN_GROUP;
 #pragma unroll
                 for (int k = 0; k < 4; ++k)
@@ -142,8 +143,7 @@ __global__ void __launch_bounds__(DN_THREADS) dense_i8_kernel(const DenseParams 
         bool alive = true;
         uint16_t sw_next = 0;
         int z_next = 0;
-#pragma unroll
-        for (int i = 0; i < DN_STAGES - 1; ++i) fetch(i);
+        fetch(0);
 #pragma unroll 1
         for (int i = 0; i <= ktot && alive; ++i) {
             // scale and zero point of the group folded in this iteration (loaded one iteration ago, behind the proxy fence:
@@ -152,11 +152,12 @@ __global__ void __launch_bounds__(DN_THREADS) dense_i8_kernel(const DenseParams 
             const int z = z_next;
             if (i < ktot) {
                 const int st = i & 1;
-                // group i has landed (this thread's copies; the two younger groups may still be in flight). The A tile's
-                // previous MMAs (group i - 2) were seen complete when this thread folded that group.
-                cp_async_wait<DN_STAGES - 2>();
+                // group i has landed (this thread's copies; nothing else is in flight: a proxy fence with copies in flight
+                // would wait for them). The A tile's previous MMAs (group i - 2) were seen complete when this thread folded
+                // that group.
+                cp_async_wait<0>();
                 uint8_t* As = smem + DN_SM_A + st * DN_A_BYTES;
-                const uint4* raw = reinterpret_cast<const uint4*>(smem + DN_SM_RAW + (i & (DN_STAGES - 1)) * DN_RAW_BYTES + 64 * tid);
+                const uint4* raw = reinterpret_cast<const uint4*>(smem + DN_SM_RAW + 64 * tid);
                 // weights: each task yields 8 words for row g of its strip and 8 for row g + 8, stored at the codes'
                 // fragment positions
 #pragma unroll
@@ -174,6 +175,8 @@ __global__ void __launch_bounds__(DN_THREADS) dense_i8_kernel(const DenseParams 
                 }
                 ptx::fence_proxy_async_smem();         // the A tile, and the activation tile the copies wrote, for the tensor core
                 ptx::mbar_arrive(BAR(DB_FULL + st));
+                // group i + 1 comes in while group i - 1 is folded; its slots were last read by the MMAs of group i - 2
+                fetch(i + 1);
                 sw_next = __ldg(reinterpret_cast<const uint16_t*>(my_meta + size_t(i) * DN_META_BYTES));
                 z_next = int(__ldg(my_zero + size_t(i) * DN_META_BYTES));
             }
@@ -193,18 +196,24 @@ __global__ void __launch_bounds__(DN_THREADS) dense_i8_kernel(const DenseParams 
                     ptx::tmem_ld32(tmem + (uint32_t(warp * 32) << 16) + st * DN_TOK + 32 * h, d);
                     ptx::tmem_wait_ld();
 #pragma unroll
-                    for (int n = 0; n < 32; ++n) {
-                        // int -> float through the float whose bits are 1.5 * 2^23 + v: exact for |v| < 2^22 (here
-                        // |v| <= 255 * 127 * 128), one integer add and one float subtract at full rate
-                        const int v = int(d[n]) - z * sq[32 * h + n];
-                        const float vf = __int_as_float(v + 0x4B400000) - 12582912.0f;
-                        c[32 * h + n] = __fmaf_rn(__fmul_rn(sw, sx[32 * h + n]), vf, c[32 * h + n]);
+                    for (int n4 = 0; n4 < 32; n4 += 4) {
+                        const float4 sx4 = *reinterpret_cast<const float4*>(sx + 32 * h + n4);      // broadcast 16-byte loads
+                        const int4 sq4 = *reinterpret_cast<const int4*>(sq + 32 * h + n4);
+                        const float sxv[4] = {sx4.x, sx4.y, sx4.z, sx4.w};
+                        const int sqv[4] = {sq4.x, sq4.y, sq4.z, sq4.w};
+#pragma unroll
+                        for (int e = 0; e < 4; ++e) {
+                            // int -> float through the float whose bits are 1.5 * 2^23 + v: exact for |v| < 2^22 (here
+                            // |v| <= 255 * 127 * 128), integer adds and one float subtract at full rate
+                            const int n = n4 + e;
+                            const int v = int(d[n]) - z * sqv[e];
+                            const float vf = __int_as_float(v + 0x4B400000) - 12582912.0f;
+                            c[32 * h + n] = __fmaf_rn(__fmul_rn(sw, sxv[e]), vf, c[32 * h + n]);
+                        }
                     }
                 }
                 ptx::tc_fence_before();
             }
-            // the slots of group i - 1 (activation tile read by its MMAs, now complete) take group i + 3
-            fetch(i + DN_STAGES - 1);
         }
         cp_async_wait<0>();
         if (alive) {
@@ -232,7 +241,7 @@ __global__ void __launch_bounds__(DN_THREADS) dense_i8_kernel(const DenseParams 
             ptx::tc_fence_after();
             if (ptx::elect_one()) {
                 const uint32_t a_s = ptx::smem_u32(smem + DN_SM_A + st * DN_A_BYTES);
-                const uint32_t b_s = ptx::smem_u32(smem + DN_SM_B + (i & (DN_STAGES - 1)) * DN_B_BYTES);
+                const uint32_t b_s = ptx::smem_u32(smem + DN_SM_B + (i % DN_STAGES) * DN_B_BYTES);
 #pragma unroll
                 for (int k = 0; k < 4; ++k)
                     mma_i8_ss(tmem + st * DN_TOK, ptx::smem_desc_sw128(a_s + 32 * k, 16, 1024), ptx::smem_desc_sw128(b_s + 32 * k, 16, 1024), id, k > 0);
