@@ -165,13 +165,16 @@ __global__ void __launch_bounds__(DN_THREADS) dense_i8_kernel(const DenseParams 
                     const uint4 lo = raw[2 * task], h4 = raw[2 * task + 1];
                     const uint32_t w[8] = {lo.x, lo.y, lo.z, lo.w, h4.x, h4.y, h4.z, h4.w};
                     const int ra = (sl0 + 4 * task) * 16 + g, rb = ra + 8;            // rows inside the CTA tile
-#pragma unroll
-                    for (int k = 0; k < 8; ++k) {
-                        const int pos = 32 * t + 8 * (k >> 1) + 4 * (k & 1);
-                        const int chunk = pos >> 4, within = pos & 15;
-                        *reinterpret_cast<uint32_t*>(As + ra * 128 + ((chunk ^ (ra & 7)) << 4) + within) = w[k] & 0x0F0F0F0Fu;
-                        *reinterpret_cast<uint32_t*>(As + rb * 128 + ((chunk ^ (rb & 7)) << 4) + within) = (w[k] >> 4) & 0x0F0F0F0Fu;
-                    }
+                    // word k holds the codes at fragment positions 32 t + 8 (k / 2) + 4 (k % 2): words 0-3 are the 16-byte chunk
+                    // 2 t of the row, words 4-7 chunk 2 t + 1. Two 16-byte stores per row; a quarter warp covers eight
+                    // different chunk positions, so they are conflict-free.
+                    const uint32_t m = 0x0F0F0F0Fu;
+                    *reinterpret_cast<uint4*>(As + ra * 128 + (((2 * t) ^ (ra & 7)) << 4)) = make_uint4(w[0] & m, w[1] & m, w[2] & m, w[3] & m);
+                    *reinterpret_cast<uint4*>(As + ra * 128 + (((2 * t + 1) ^ (ra & 7)) << 4)) = make_uint4(w[4] & m, w[5] & m, w[6] & m, w[7] & m);
+                    *reinterpret_cast<uint4*>(As + rb * 128 + (((2 * t) ^ (rb & 7)) << 4)) =
+                        make_uint4((w[0] >> 4) & m, (w[1] >> 4) & m, (w[2] >> 4) & m, (w[3] >> 4) & m);
+                    *reinterpret_cast<uint4*>(As + rb * 128 + (((2 * t + 1) ^ (rb & 7)) << 4)) =
+                        make_uint4((w[4] >> 4) & m, (w[5] >> 4) & m, (w[6] >> 4) & m, (w[7] >> 4) & m);
                 }
                 ptx::fence_proxy_async_smem();         // the A tile, and the activation tile the copies wrote, for the tensor core
                 ptx::mbar_arrive(BAR(DB_FULL + st));
