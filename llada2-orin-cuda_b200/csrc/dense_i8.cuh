@@ -78,7 +78,7 @@ __global__ void __launch_bounds__(DN_THREADS) dense_i8_kernel(const DenseParams 
     __shared__ uint32_t tmem_slot;
     __shared__ int abort_flag_s;
     volatile int* abort_flag = &abort_flag_s;
-    const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+    const int tid = threadIdx.x, warp = tid >> 5;
     const int row0 = blockIdx.x * DN_ROWS, n0 = blockIdx.y * DN_TOK;
     const int ktot = p.K / DN_GROUP;
     const uint32_t bar0 = ptx::smem_u32(smem + DN_SM_BAR);
