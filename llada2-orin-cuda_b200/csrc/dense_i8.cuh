@@ -140,6 +140,7 @@ __global__ void __launch_bounds__(DN_THREADS) dense_i8_kernel(const DenseParams 
         float c[DN_TOK];
 #pragma unroll
         for (int n = 0; n < DN_TOK; ++n) c[n] = 0.f;
+        const bool second_half = p.ntokens - n0 > 32;
         bool alive = true;
         uint16_t sw_next = 0;
         int z_next = 0;
@@ -195,6 +196,7 @@ __global__ void __launch_bounds__(DN_THREADS) dense_i8_kernel(const DenseParams 
                 const int* sq = reinterpret_cast<const int*>(smem + DN_SM_SQ) + (gi & 7) * DN_TOK;
 #pragma unroll
                 for (int h = 0; h < 2; ++h) {
+                    if (h == 1 && !second_half) break;       // a tile with at most 32 live tokens (the reference's decode shape)
                     uint32_t d[32];
                     ptx::tmem_ld32(tmem + (uint32_t(warp * 32) << 16) + st * DN_TOK + 32 * h, d);
                     ptx::tmem_wait_ld();
