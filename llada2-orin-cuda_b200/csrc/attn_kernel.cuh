@@ -13,8 +13,9 @@
 //                   exactly the fp16 P the numerator uses (numerator and denominator then share their rounding)
 //   softmax warps : one thread per query row (TMEM lane); row max, lazy rescale (the reference maximum moves only
 //                   when exceeded by more than 8 in log2 units, engine/attn.cu:237-255), p = 2^(s*scale*log2e - m),
-//                   P stored back over S in TMEM as fp16 pairs (keys 0-63 at columns 0-31, keys 64-127 at 64-95: each
-//                   softmax warp overwrites only S columns it has itself consumed)
+//                   P stored back over S in TMEM as fp16 pairs (the 32 keys of chunk g at columns 32 g .. 32 g + 15, the
+//                   first half of the S columns they were computed from: a softmax warp overwrites only S columns it
+//                   has itself consumed)
 // The run's un-normalised O (fp32), reference maximum (log2 units) and row sum go to a partial slot in the format of
 // the reference's Opart/Mpart/Lpart (engine/attn.cu:291-305); merge_kernel.cuh folds the slots of a tile together.
 //
@@ -69,15 +70,21 @@ constexpr int SM_BAR = SM_RAW + NRAW * RAW_STRIDE;
 constexpr int SM_X = SM_BAR + 512;                 // row-max exchange between the two softmax warps of a lane quarter
 constexpr int SM_MISC = SM_X + 2 * 4 * 128 * 4;
 constexpr int ATTN_SMEM_BYTES = SM_MISC + 16;
-// warps 0-7 softmax (warp w: TMEM lane quarter w % 4, key half w / 4), 8-23 dequant (four groups of four warps, group g
-// takes unit g of every tile), 24 producer, 25 S-MMA issue, 26 PV-MMA issue
+// warps 0-7 softmax (warp w: TMEM lane quarter w % 4, key half w / 4), 8-15 dequant (two groups of four warps, group g
+// takes units g and g + 2 of every tile), then producer, S-MMA issue, PV-MMA issue. The warp counts are the measured
+// optimum: the kernel is bound by instruction issue, every warp pays a fixed number of hand-off instructions per tile,
+// so fewer, busier dequantising warps win (16 of them: +4 % time), while a single group or four softmax warps leave too
+// little latency hiding (+40 % / +12 %) and sixteen softmax warps pay too many hand-offs (+8 %).
 #ifndef LLATTN_DEQUANT_WARPS
-#define LLATTN_DEQUANT_WARPS 16
+#define LLATTN_DEQUANT_WARPS 8
 #endif
-constexpr int SOFTMAX_WARPS = 8, DEQUANT_WARPS = LLATTN_DEQUANT_WARPS, DEQUANT_GROUPS = DEQUANT_WARPS / 4;
+#ifndef LLATTN_SOFTMAX_WARPS
+#define LLATTN_SOFTMAX_WARPS 8
+#endif
+constexpr int SOFTMAX_WARPS = LLATTN_SOFTMAX_WARPS, KEY_PARTS = SOFTMAX_WARPS / 4, DEQUANT_WARPS = LLATTN_DEQUANT_WARPS, DEQUANT_GROUPS = DEQUANT_WARPS / 4;
 constexpr int WARP_SERVICE = SOFTMAX_WARPS + DEQUANT_WARPS;
 constexpr int WARP_PRODUCER = WARP_SERVICE, WARP_MMA = WARP_SERVICE + 1, WARP_MMA_PV = WARP_SERVICE + 2;
-constexpr int ATTN_THREADS = 32 * (WARP_SERVICE + 3);  // 864
+constexpr int ATTN_THREADS = 32 * (WARP_SERVICE + 3);  // 608
 constexpr int TMEM_COLS = 512;
 constexpr int TM_S = 0, TM_O = 256, TM_L = TM_O + 128, TM_Q = 400;   // S at columns 0 and 128, O at 256..383, row sum at 384, Q at 400..463
 constexpr float RESCALE_SLACK = 8.f;
@@ -88,6 +95,8 @@ enum { B_RAW_FULL = 0, B_RAW_EMPTY = B_RAW_FULL + NRAW, B_K_FULL = B_RAW_EMPTY +
        B_Q_FULL = B_P_FULL + 2, B_O_FREE, B_SPARE, B_XCHG = B_SPARE + 2, B_COUNT = B_XCHG + 4 };
 static_assert(B_COUNT * 8 <= 512, "barrier area");
 static_assert(ATTN_SMEM_BYTES <= 232448, "shared memory budget");
+static_assert(SOFTMAX_WARPS == 4 || SOFTMAX_WARPS == 8 || SOFTMAX_WARPS == 16, "softmax warps: 1, 2 or 4 per TMEM lane quarter");
+static_assert(DEQUANT_GROUPS >= 1 && TILE_UNITS % DEQUANT_GROUPS == 0 && DEQUANT_WARPS % 4 == 0, "dequant warps: groups of four, 1, 2 or 4 groups");
 
 struct KParams {
     const SeqDesc* seqs;           // list mode
@@ -284,7 +293,7 @@ __device__ __forceinline__ void attn_tile_body(const KParams& p, const int cta) 
         ptx::mbar_init(BAR(B_Q_FULL), 32 * SOFTMAX_WARPS); ptx::mbar_init(BAR(B_O_FREE), 32 * SOFTMAX_WARPS);
         ptx::mbar_init(BAR(B_SPARE), 1);
         ptx::mbar_init(BAR(B_SPARE + 1), 1);
-        for (int i = 0; i < 4; ++i) ptx::mbar_init(BAR(B_XCHG + i), 64);
+        for (int i = 0; i < 4; ++i) ptx::mbar_init(BAR(B_XCHG + i), 32 * KEY_PARTS);
         ptx::fence_mbar_init();
         *abort_flag = 0;
     }
@@ -302,8 +311,11 @@ __device__ __forceinline__ void attn_tile_body(const KParams& p, const int cta) 
 
     if (warp < SOFTMAX_WARPS) {
         // ================================================================== softmax + epilogue
-        // thread = (query row, key half): the warp pair (w, w ^ 4) shares TMEM lanes and splits a tile's keys 0-63 / 64-127
-        const int q = warp & 3, hf = warp >> 2, row = q * 32 + lane;
+        // thread = (query row, key part): the KEY_PARTS warps of a TMEM lane quarter split a tile's four 32-key chunks
+        // (chunk g = S columns [32 g, 32 g + 32); its P goes to the first 16 of the same columns, so a warp only ever
+        // overwrites S it has itself consumed), the channels of Q and the columns of O
+        constexpr int CPW = 4 / KEY_PARTS;            // chunks per warp and tile = 32-column groups of O per warp
+        const int q = warp & 3, kp = warp >> 2, row = q * 32 + lane;
         const uint32_t tlane = tmem + (uint32_t(q * 32) << 16);
         float* xb = reinterpret_cast<float*>(smem + SM_X);
         uint32_t t = 0;
@@ -314,16 +326,19 @@ __device__ __forceinline__ void attn_tile_body(const KParams& p, const int cta) 
             if (!fetch_item(p, ii, w, s)) continue;
             const int U = w.rec_count + w.fresh, ntiles = (U + TILE_UNITS - 1) / TILE_UNITS;
             float mref = -INFINITY;
-            {   // this thread's query row, channels [64 hf, 64 hf + 64), into tensor memory as fp16 pairs. Every S MMA of
-                // the previous item has completed: this warp has seen the S of its last tile.
-                const half* src = p.Q + ((size_t(s.q_first + w.qblk) * BLK + (row >> 2)) * NQH + 4 * w.kvh + (row & 3)) * D + 64 * hf;
-                uint32_t r[32];
+            {   // this thread's query row, channels [32 CPW kp, 32 CPW (kp + 1)), into tensor memory as fp16 pairs. Every S
+                // MMA of the previous item has completed: this warp has seen the S of its last tile.
+                const half* src = p.Q + ((size_t(s.q_first + w.qblk) * BLK + (row >> 2)) * NQH + 4 * w.kvh + (row & 3)) * D + 32 * CPW * kp;
+#pragma unroll 1
+                for (int c = 0; c < CPW; ++c) {
+                    uint32_t r[16];
 #pragma unroll
-                for (int g = 0; g < 8; ++g) {
-                    const uint4 v = permute8(__ldg(reinterpret_cast<const uint4*>(src + 8 * g)));
-                    r[4 * g] = v.x; r[4 * g + 1] = v.y; r[4 * g + 2] = v.z; r[4 * g + 3] = v.w;
+                    for (int g = 0; g < 4; ++g) {
+                        const uint4 v = permute8(__ldg(reinterpret_cast<const uint4*>(src + 32 * c + 8 * g)));
+                        r[4 * g] = v.x; r[4 * g + 1] = v.y; r[4 * g + 2] = v.z; r[4 * g + 3] = v.w;
+                    }
+                    ptx::tmem_st16(tlane + TM_Q + 16 * (CPW * kp + c), r);
                 }
-                ptx::tmem_st32(tlane + TM_Q + 32 * hf, r);
                 ptx::tmem_wait_st();
                 ptx::tc_fence_before();
                 ptx::mbar_arrive(BAR(B_Q_FULL));
@@ -331,17 +346,17 @@ __device__ __forceinline__ void attn_tile_body(const KParams& p, const int cta) 
 #pragma unroll 1
             for (int i = 0; i < ntiles; ++i, ++t) {
                 const int b = t & 1, nu = min(TILE_UNITS, U - TILE_UNITS * i);
-                const int nc = max(0, min(2, nu - 2 * hf));          // 32-key chunks of this tile this warp owns
+                const int nc = max(0, min(CPW, nu - CPW * kp));          // 32-key chunks of this tile this warp owns
                 LLATTN_TR(1, t);
                 if (!ptx::mbar_wait(BAR(B_S_FULL + b), (t >> 1) & 1, abort_flag)) { alive = false; errbits |= ERR_WAIT_SOFTMAX; break; }
                 LLATTN_TR(2, t);
                 ptx::tc_fence_after();
-                const uint32_t ts = tlane + TM_S + b * 128;
+                const uint32_t ts = tlane + TM_S + b * 128 + 32 * CPW * kp;
                 float mx = -INFINITY;
 #pragma unroll 1
                 for (int c = 0; c < nc; ++c) {
                     uint32_t r[32];
-                    ptx::tmem_ld32(ts + 64 * hf + 32 * c, r);
+                    ptx::tmem_ld32(ts + 32 * c, r);
                     ptx::tmem_wait_ld();
 #pragma unroll
                     for (int j = 0; j < 32; j += 2) {
@@ -349,32 +364,36 @@ __device__ __forceinline__ void attn_tile_body(const KParams& p, const int cta) 
                         else mx = max3(mx, __uint_as_float(r[j]), __uint_as_float(r[j + 1]));
                     }
                 }
-                // row max over both halves: exchange through shared memory with the partner warp (double-buffered by
-                // tile parity; the pair's mbarrier, one phase per tile, orders write -> read and its wait is bounded)
+                // row max over all parts: exchange through shared memory with the other warps of the lane quarter
+                // (double-buffered by tile parity; the quarter's mbarrier, one phase per tile, orders write -> read and
+                // its wait is bounded)
                 LLATTN_TR(5, t);
-                xb[b * 256 + hf * 128 + row] = mx;
-                ptx::mbar_arrive(BAR(B_XCHG + q));
-                if (!ptx::mbar_wait(BAR(B_XCHG + q), t & 1, abort_flag)) { alive = false; errbits |= ERR_WAIT_SOFTMAX; break; }
-                mx = fmaxf(mx, xb[b * 256 + (hf ^ 1) * 128 + row]);
+                if (KEY_PARTS > 1) {
+                    xb[b * 512 + kp * 128 + row] = mx;
+                    ptx::mbar_arrive(BAR(B_XCHG + q));
+                    if (!ptx::mbar_wait(BAR(B_XCHG + q), t & 1, abort_flag)) { alive = false; errbits |= ERR_WAIT_SOFTMAX; break; }
+#pragma unroll
+                    for (int k = 1; k < KEY_PARTS; ++k) mx = fmaxf(mx, xb[b * 512 + ((kp + k) % KEY_PARTS) * 128 + row]);
+                }
                 LLATTN_TR(3, t);
                 const float msc = mx * p.sl2;
                 const bool moved = msc > mref + RESCALE_SLACK;
                 if (i > 0 && __any_sync(0xffffffffu, moved)) {
-                    // the accumulated O of these rows is rescaled to the new reference maximum (this warp's half of the
+                    // the accumulated O of these rows is rescaled to the new reference maximum (this warp's share of the
                     // columns); every PV issued so far must have landed first
                     if (!ptx::mbar_wait(BAR(B_PV_DONE + (b ^ 1)), ((t - 1) >> 1) & 1, abort_flag)) { alive = false; errbits |= ERR_WAIT_SOFTMAX; break; }
                     ptx::tc_fence_after();
                     const float corr = moved ? ex2(mref - msc) : 1.f;
 #pragma unroll 1
-                    for (int c = 0; c < 2; ++c) {
+                    for (int c = 0; c < CPW; ++c) {
                         uint32_t r[32];
-                        ptx::tmem_ld32(tlane + TM_O + 64 * hf + 32 * c, r);
+                        ptx::tmem_ld32(tlane + TM_O + 32 * (CPW * kp + c), r);
                         ptx::tmem_wait_ld();
 #pragma unroll
                         for (int j = 0; j < 32; ++j) r[j] = __float_as_uint(__uint_as_float(r[j]) * corr);
-                        ptx::tmem_st32(tlane + TM_O + 64 * hf + 32 * c, r);
+                        ptx::tmem_st32(tlane + TM_O + 32 * (CPW * kp + c), r);
                     }
-                    if (hf == 1) {
+                    if (kp == KEY_PARTS - 1) {
                         uint32_t r[16];
                         ptx::tmem_ld16(tlane + TM_L, r);
                         ptx::tmem_wait_ld();
@@ -388,7 +407,7 @@ __device__ __forceinline__ void attn_tile_body(const KParams& p, const int cta) 
 #pragma unroll 1
                 for (int c = 0; c < nc; ++c) {
                     uint32_t r[32], pk[16];
-                    ptx::tmem_ld32(ts + 64 * hf + 32 * c, r);
+                    ptx::tmem_ld32(ts + 32 * c, r);
                     ptx::tmem_wait_ld();
 #pragma unroll
                     for (int j = 0; j < 16; ++j) {
@@ -398,7 +417,7 @@ __device__ __forceinline__ void attn_tile_body(const KParams& p, const int cta) 
                         const half2 h = __floats2half2_rn(ex2(x0), ex2(x1));
                         pk[j] = *reinterpret_cast<const uint32_t*>(&h);
                     }
-                    ptx::tmem_st16(ts + 64 * hf + 16 * c, pk);      // P chunk over S columns this warp has already consumed
+                    ptx::tmem_st16(ts + 32 * c, pk);      // P chunk over the S columns it was computed from
                 }
                 ptx::tmem_wait_st();
                 ptx::tc_fence_before();
@@ -406,15 +425,15 @@ __device__ __forceinline__ void attn_tile_body(const KParams& p, const int cta) 
                 LLATTN_TR(4, t);
             }
             if (!alive) break;
-            // ---- epilogue: un-normalised O (this warp's half of the columns), reference maximum and row sum of the run
+            // ---- epilogue: un-normalised O (this warp's share of the columns), reference maximum and row sum of the run
             const uint32_t tl = t - 1;
             if (!ptx::mbar_wait(BAR(B_PV_DONE + (tl & 1)), (tl >> 1) & 1, abort_flag)) { alive = false; errbits |= ERR_WAIT_SOFTMAX; break; }
             ptx::tc_fence_after();
-            float* orow = p.Opart + (size_t(w.slot) * QR + row) * D + 64 * hf;
+            float* orow = p.Opart + (size_t(w.slot) * QR + row) * D + 32 * CPW * kp;
 #pragma unroll 1
-            for (int c = 0; c < 2; ++c) {
+            for (int c = 0; c < CPW; ++c) {
                 uint32_t r[32];
-                ptx::tmem_ld32(tlane + TM_O + 64 * hf + 32 * c, r);
+                ptx::tmem_ld32(tlane + TM_O + 32 * (CPW * kp + c), r);
                 ptx::tmem_wait_ld();
 #pragma unroll
                 for (int g = 0; g < 4; ++g) {      // positions (0..7) hold dims (0,4,1,5,2,6,3,7)
@@ -426,14 +445,13 @@ __device__ __forceinline__ void attn_tile_body(const KParams& p, const int cta) 
                     *reinterpret_cast<float4*>(orow + 32 * c + 8 * g + 4) = hi;
                 }
             }
-            if (hf == 1) {
+            if (kp == KEY_PARTS - 1) {
                 uint32_t r[16];
                 ptx::tmem_ld16(tlane + TM_L, r);
                 ptx::tmem_wait_ld();
                 p.Lpart[size_t(w.slot) * QR + row] = __uint_as_float(r[0]);
-            } else {
-                p.Mpart[size_t(w.slot) * QR + row] = mref;
             }
+            if (kp == 0) p.Mpart[size_t(w.slot) * QR + row] = mref;
             ptx::tc_fence_before();
             ptx::mbar_arrive(BAR(B_O_FREE));
         }
@@ -458,27 +476,36 @@ __device__ __forceinline__ void attn_tile_body(const KParams& p, const int cta) 
             const int U = w.rec_count + w.fresh, ntiles = (U + TILE_UNITS - 1) / TILE_UNITS;
             const size_t f0 = (size_t(s.q_first + w.qblk) * BLK) * NKV * D + size_t(w.kvh) * D;
             int i = 0;
-            // ---- steady state: tiles made of four committed records. This group's unit is always there, nothing is
+            // ---- steady state: tiles made of four committed records. This group's units are always there, nothing is
             // decided per tile, and the loop carries only what changes (tile count, record count).
-            const int nfull = DEQUANT_GROUPS == TILE_UNITS ? w.rec_count / TILE_UNITS : 0;
+            const int nfull = w.rec_count / TILE_UNITS;
 #pragma unroll 1
             for (; i < nfull; ++i, ++t) {
                 const uint32_t b = t & 1, freed = ((t >> 1) - 1) & 1;      // phase in which tile t-2 let go of its buffers
-                const uint32_t rr = r + grp, slot = rr % NRAW;
-                const uint8_t* raw = smem + SM_RAW + slot * RAW_STRIDE;
                 LLATTN_TR(10, t);
                 if (t >= 2 && !ptx::mbar_wait(BAR(B_K_FREE + b), freed, abort_flag)) { alive = false; errbits |= ERR_WAIT_DEQUANT; break; }
                 LLATTN_TR(15, t);
-                if (!ptx::mbar_wait(BAR(B_RAW_FULL + slot), (rr / NRAW) & 1, abort_flag)) { alive = false; errbits |= ERR_WAIT_DEQUANT; break; }
+#pragma unroll
+                for (int u = 0; u < TILE_UNITS / DEQUANT_GROUPS; ++u) {
+                    const uint32_t rr = r + grp + u * DEQUANT_GROUPS, slot = rr % NRAW;
+                    if (!ptx::mbar_wait(BAR(B_RAW_FULL + slot), (rr / NRAW) & 1, abort_flag)) { alive = false; errbits |= ERR_WAIT_DEQUANT; break; }
+                    if (!(LLATTN_SKIP & 1))
+                        dequant_k(smem + SM_RAW + slot * RAW_STRIDE, smem + SM_K + b * TILE_BYTES + (grp + u * DEQUANT_GROUPS) * UNIT_BYTES, dq);
+                }
+                if (!alive) break;
                 LLATTN_TR(16, t);
-                if (!(LLATTN_SKIP & 1)) dequant_k(raw, smem + SM_K + b * TILE_BYTES + grp * UNIT_BYTES, dq);
                 ptx::fence_proxy_async_smem();
                 ptx::mbar_arrive(BAR(B_K_FULL + b));
                 LLATTN_TR(12, t);
                 if (t >= 2 && !ptx::mbar_wait(BAR(B_PV_DONE + b), freed, abort_flag)) { alive = false; errbits |= ERR_WAIT_DEQUANT; break; }
                 LLATTN_TR(13, t);
-                if (!(LLATTN_SKIP & 1)) dequant_v(raw, smem + SM_V + b * VTILE_BYTES + grp * UNIT_BYTES, dq);
-                ptx::mbar_arrive(BAR(B_RAW_EMPTY + slot));
+#pragma unroll
+                for (int u = 0; u < TILE_UNITS / DEQUANT_GROUPS; ++u) {
+                    const uint32_t rr = r + grp + u * DEQUANT_GROUPS, slot = rr % NRAW;
+                    if (!(LLATTN_SKIP & 1))
+                        dequant_v(smem + SM_RAW + slot * RAW_STRIDE, smem + SM_V + b * VTILE_BYTES + (grp + u * DEQUANT_GROUPS) * UNIT_BYTES, dq);
+                    ptx::mbar_arrive(BAR(B_RAW_EMPTY + slot));
+                }
                 ptx::fence_proxy_async_smem();
                 ptx::mbar_arrive(BAR(B_V_FULL + b));
                 LLATTN_TR(14, t);
@@ -632,7 +659,7 @@ __device__ __forceinline__ void attn_tile_body(const KParams& p, const int cta) 
                 if (i == 0 && itc > 0 && !uniform_i32(ptx::mbar_wait(BAR(B_O_FREE), (itc - 1) & 1, abort_flag))) { alive = false; errbits |= ERR_WAIT_MMA; break; }
                 ptx::tc_fence_after();
                 {
-                    // unit u = keys 32u..32u+31 = K-steps 2u, 2u+1; its P sits at columns (u >> 1) * 64 + (u & 1) * 16 of the S buffer
+                    // unit u = keys 32u..32u+31 = K-steps 2u, 2u+1; its P sits at columns 32u .. 32u+15 of the S buffer
                     const uint32_t pb = tmem + TM_S + b * 128, vlo = b ? vlo1 : vlo0;
                     if (nu == TILE_UNITS) {
                         ptx::mma_ts_pv8_warp(tmem + TM_O, pb, vlo, vhi, idO, i == 0 ? 0u : 1u, BAR(B_PV_DONE + b));
@@ -641,7 +668,7 @@ __device__ __forceinline__ void attn_tile_body(const KParams& p, const int cta) 
                         for (int u = 0; u < TILE_UNITS - 1; ++u)
                             if (u < nu) {
                                 const uint64_t d0 = (uint64_t(vhi) << 32) | (vlo + 256u * u);
-                                ptx::mma_ts_x2_warp(tmem + TM_O, pb + (u >> 1) * 64 + (u & 1) * 16, d0, d0 + 128, idO, (i == 0 && u == 0) ? 0u : 1u);
+                                ptx::mma_ts_x2_warp(tmem + TM_O, pb + 32 * u, d0, d0 + 128, idO, (i == 0 && u == 0) ? 0u : 1u);
                             }
                         ptx::mma_commit_warp(BAR(B_PV_DONE + b));
                     }

@@ -222,7 +222,7 @@ __device__ __forceinline__ void mma_ts_s8_warp(uint32_t d_tmem, uint32_t a_tmem,
         : "memory");
 }
 // O (+)= P V over a full tile of four 32-key units from one base descriptor: K-step j (16 keys) adds 128 16-byte units;
-// the P of unit u sits at columns (u >> 1) * 64 + (u & 1) * 16 of the S buffer, 8 columns per K-step. One commit.
+// the P of unit u sits at columns 32u .. 32u+15 of the S buffer, 8 columns per K-step. One commit.
 __device__ __forceinline__ void mma_ts_pv8_warp(uint32_t d_tmem, uint32_t p_tmem, uint32_t b_lo, uint32_t b_hi, uint32_t idesc,
                                                 uint32_t accumulate_first, uint32_t bar) {
     asm volatile(
@@ -233,17 +233,17 @@ __device__ __forceinline__ void mma_ts_pv8_warp(uint32_t d_tmem, uint32_t p_tmem
         "@pe tcgen05.mma.cta_group::1.kind::f16 [%0], [%1], db, %4, pa;\n\t"
         "add.u32 a, %1, 8;\n\t add.u32 l, %2, 128;\n\t mov.b64 db, {l, %3};\n\t"
         "@pe tcgen05.mma.cta_group::1.kind::f16 [%0], [a], db, %4, pt;\n\t"
-        "add.u32 a, %1, 16;\n\t add.u32 l, %2, 256;\n\t mov.b64 db, {l, %3};\n\t"
+        "add.u32 a, %1, 32;\n\t add.u32 l, %2, 256;\n\t mov.b64 db, {l, %3};\n\t"
         "@pe tcgen05.mma.cta_group::1.kind::f16 [%0], [a], db, %4, pt;\n\t"
-        "add.u32 a, %1, 24;\n\t add.u32 l, %2, 384;\n\t mov.b64 db, {l, %3};\n\t"
+        "add.u32 a, %1, 40;\n\t add.u32 l, %2, 384;\n\t mov.b64 db, {l, %3};\n\t"
         "@pe tcgen05.mma.cta_group::1.kind::f16 [%0], [a], db, %4, pt;\n\t"
         "add.u32 a, %1, 64;\n\t add.u32 l, %2, 512;\n\t mov.b64 db, {l, %3};\n\t"
         "@pe tcgen05.mma.cta_group::1.kind::f16 [%0], [a], db, %4, pt;\n\t"
         "add.u32 a, %1, 72;\n\t add.u32 l, %2, 640;\n\t mov.b64 db, {l, %3};\n\t"
         "@pe tcgen05.mma.cta_group::1.kind::f16 [%0], [a], db, %4, pt;\n\t"
-        "add.u32 a, %1, 80;\n\t add.u32 l, %2, 768;\n\t mov.b64 db, {l, %3};\n\t"
+        "add.u32 a, %1, 96;\n\t add.u32 l, %2, 768;\n\t mov.b64 db, {l, %3};\n\t"
         "@pe tcgen05.mma.cta_group::1.kind::f16 [%0], [a], db, %4, pt;\n\t"
-        "add.u32 a, %1, 88;\n\t add.u32 l, %2, 896;\n\t mov.b64 db, {l, %3};\n\t"
+        "add.u32 a, %1, 104;\n\t add.u32 l, %2, 896;\n\t mov.b64 db, {l, %3};\n\t"
         "@pe tcgen05.mma.cta_group::1.kind::f16 [%0], [a], db, %4, pt;\n\t"
         "@pe tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%6];\n\t"
         "}\n"

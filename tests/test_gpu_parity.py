@@ -254,6 +254,33 @@ def test_many_short_items_per_cta(api, ctx, orc, pkg):
         assert np.abs(res["LSE"][sl] - Lw).max() <= TOL_LSE, i
 
 
+@pytest.mark.parametrize("pattern", ["rising", "falling", "second_half", "alternating"])
+def test_moving_row_maximum(api, ctx, orc, pkg, pattern):
+    """Scores whose row maximum moves by many powers of two from one 32-key block to the next: the running reference
+    maximum is raised again and again (accumulator rescale), in one half of a 128-key tile only (the two softmax warps
+    of a row start from different tentative references), or never after the first tile. K of block j is a multiple
+    g[j] of one direction plus noise, Q points along that direction, so the score level of block j is about g[j] * 5
+    in log2 units."""
+    n = 37
+    wl = pkg.workload
+    Kc, Vc = wl.context_blocks(n, seq=900)
+    Q, Kf, Vf = wl.query_blocks(1, seq=900)
+    u = np.sign(np.random.default_rng(5).standard_normal(128)).astype(np.float32)
+    j = np.arange(n, dtype=np.float32)
+    g = {"rising": j * 0.5, "falling": (n - j) * 0.5, "second_half": np.where((j % 4) >= 2, 4.0, 0.0) + j * 0.05,
+         "alternating": np.where((j // 4) % 2 == 0, 0.0, 6.0) * (1 + j / n)}[pattern]
+    Kc = (Kc.astype(np.float32) * 0.25 + g[:, None, None, None] * u * 0.35).astype(np.float16)
+    Q = (Q.astype(np.float32) * 0.25 + u * 1.0).astype(np.float16)
+    Kf = (Kf.astype(np.float32) * 0.25).astype(np.float16)
+    cache = np.zeros((4, n + 1, orc.REC_BYTES), np.uint8)
+    orc.kv_commit(Kc, Vc, cache, n + 1, 0)
+    res = run_batched(api, ctx, [(Q, Kf, Vf, cache, n + 1, n)])
+    O1, L1 = orc.attention(Q, Kf, Vf, cache, n + 1, n, dq_mode=1)
+    assert np.isfinite(res["O32"]).all()
+    assert relmax(res["O32"], O1) <= TOL_O and rel_l2(res["O32"], O1) <= 2 * TOL_L2
+    assert np.abs(res["LSE"] - L1).max() <= 2 * TOL_LSE
+
+
 def test_paged_cache(api, ctx, orc, pkg):
     n = 21
     Q, Kf, Vf, cache, maxb = make_case(pkg.workload, orc, n, seq=77)
