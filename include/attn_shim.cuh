@@ -10,7 +10,7 @@
 // nodes (:524-552), `attn::kv_commit<<<dim3(4, nb), 128>>>` (:591,:656).
 //
 // What differs from the file it replaces (all visible through the constants below):
-//   ATT_NTH is 608 and SMEM_BYTES about 203 KB (one CTA per SM; the reference ran 128 threads, 79 KB, two per SM);
+//   ATT_NTH is 640 and SMEM_BYTES about 203 KB (one CTA per SM; the reference ran 128 threads, 79 KB, two per SM);
 //   a CTA's chunk should hold a multiple of 4 blocks (128-key MMA tiles) — any blocks_per_chunk is correct, multiples
 //   of 4 are faster; and B200 wants about one chunk per SM and kv head quarter, so a caller after speed sizes its
 //   partial buffers for MAX_CHUNKS_HINT chunks (engine/engine.cu:301 sizes them for 4) and calls pick_bpc below,

@@ -4,7 +4,8 @@
 // committed records (4736 packed bytes = 32 keys each) and, on the run that ends the context, the query block's own
 // fp16 K/V. The 128 query rows of the kv head (32 tokens x 4 GQA heads) are the M dimension of every MMA.
 // Per tile of up to 4 units (128 keys):
-//   producer warp : cp.async.bulk of whole records global -> shared ring, completion on an mbarrier
+//   producer warps: cp.async.bulk of whole records global -> shared ring, completion on an mbarrier (two warps take
+//                   alternate records: one service warp per scheduler keeps the schedulers' loads alike)
 //   dequant warps : nibbles -> fp16 (magic-number unpack, one fp16 FMA per pair as the reference's __hfma2), written
 //                   straight into the no-swizzle UMMA operand layout; fresh fp16 K/V are copied into the same layout
 //   MMA warp      : S = Q K^T  (tcgen05.mma kind::f16, both operands K-major in shared memory, fp32 S in TMEM)
@@ -71,7 +72,7 @@ constexpr int SM_X = SM_BAR + 512;                 // row-max exchange between t
 constexpr int SM_MISC = SM_X + 2 * 4 * 128 * 4;
 constexpr int ATTN_SMEM_BYTES = SM_MISC + 16;
 // warps 0-7 softmax (warp w: TMEM lane quarter w % 4, key half w / 4), 8-15 dequant (two groups of four warps, group g
-// takes units g and g + 2 of every tile), then producer, S-MMA issue, PV-MMA issue. The warp counts are the measured
+// takes units g and g + 2 of every tile), then PV-MMA issue, S-MMA issue and two producers. The warp counts are the measured
 // optimum: the kernel is bound by instruction issue, every warp pays a fixed number of hand-off instructions per tile,
 // so fewer, busier dequantising warps win (16 of them: +4 % time), while a single group or four softmax warps leave too
 // little latency hiding (+40 % / +12 %) and sixteen softmax warps pay too many hand-offs (+8 %).
@@ -83,8 +84,10 @@ constexpr int ATTN_SMEM_BYTES = SM_MISC + 16;
 #endif
 constexpr int SOFTMAX_WARPS = LLATTN_SOFTMAX_WARPS, KEY_PARTS = SOFTMAX_WARPS / 4, DEQUANT_WARPS = LLATTN_DEQUANT_WARPS, DEQUANT_GROUPS = DEQUANT_WARPS / 4;
 constexpr int WARP_SERVICE = SOFTMAX_WARPS + DEQUANT_WARPS;
-constexpr int WARP_PRODUCER = WARP_SERVICE, WARP_MMA = WARP_SERVICE + 1, WARP_MMA_PV = WARP_SERVICE + 2;
-constexpr int ATTN_THREADS = 32 * (WARP_SERVICE + 3);  // 608
+// Service warps, one per scheduler (a warp runs on scheduler warp % 4 and the softmax warps cannot move): PV issue, S
+// issue and two copy producers that take alternate records, so that no scheduler carries much more than the others.
+constexpr int WARP_MMA_PV = WARP_SERVICE, WARP_MMA = WARP_SERVICE + 1, WARP_PRODUCER = WARP_SERVICE + 2, PRODUCERS = 2;
+constexpr int ATTN_THREADS = 32 * (WARP_SERVICE + 2 + PRODUCERS);  // 640
 constexpr int TMEM_COLS = 512;
 constexpr int TM_S = 0, TM_O = 256, TM_L = TM_O + 128, TM_Q = 400;   // S at columns 0 and 128, O at 256..383, row sum at 384, Q at 400..463
 constexpr float RESCALE_SLACK = 8.f;
@@ -558,9 +561,11 @@ __device__ __forceinline__ void attn_tile_body(const KParams& p, const int cta) 
                 r += uint32_t(min(nu, max(0, w.rec_count - TILE_UNITS * i)));     // records of this tile (both groups count alike)
             }
         }
-    } else if (warp == WARP_PRODUCER) {
-        // ================================================================== producer: bulk copies of records
-        uint32_t r = 0;
+    } else if (warp >= WARP_PRODUCER) {
+        // ================================================================== producers: bulk copies of records
+        // producer k takes the records whose running number r is k modulo PRODUCERS
+        const uint32_t pk = uint32_t(warp - WARP_PRODUCER);
+        uint32_t r0 = 0, last = 0, issued = 0;        // records before this item; this producer's latest record
         bool alive = true;
 #pragma unroll 1
         for (int ii = i0; ii < i1 && alive; ++ii) {
@@ -568,8 +573,8 @@ __device__ __forceinline__ void attn_tile_body(const KParams& p, const int cta) 
             if (!fetch_item(p, ii, w, s)) continue;
             const size_t hbase = size_t(w.kvh) * s.head_stride;
 #pragma unroll 1
-            for (int u = 0; u < w.rec_count; ++u, ++r) {
-                const uint32_t slot = r % NRAW;
+            for (uint32_t u = (pk - r0) % PRODUCERS; u < uint32_t(w.rec_count); u += PRODUCERS) {
+                const uint32_t r = r0 + u, slot = r % NRAW;
                 if (r >= NRAW && !ptx::mbar_wait(BAR(B_RAW_EMPTY + slot), ((r / NRAW) - 1) & 1, abort_flag)) { alive = false; errbits |= ERR_WAIT_PRODUCER; break; }
                 if (lane == 0) {
                     const size_t ridx = s.pages ? size_t(s.pages[hbase + w.rec_begin + u]) : hbase + w.rec_begin + u;
@@ -578,13 +583,15 @@ __device__ __forceinline__ void attn_tile_body(const KParams& p, const int cta) 
                                   BAR(B_RAW_FULL + slot));
                 }
                 __syncwarp();
+                last = r; ++issued;
             }
+            r0 += uint32_t(w.rec_count);
         }
         // copies still in flight must land before the shared memory is given back
         if (*abort_flag) {
-            const uint32_t n = r < NRAW ? r : NRAW;
+            const uint32_t n = issued < NRAW / PRODUCERS ? issued : NRAW / PRODUCERS;
             for (uint32_t k = 0; k < n; ++k) {
-                const uint32_t rr = r - 1 - k;
+                const uint32_t rr = last - PRODUCERS * k;
                 volatile int never = 0;
                 ptx::mbar_wait(BAR(B_RAW_FULL + rr % NRAW), (rr / NRAW) & 1, &never);
             }
