@@ -71,18 +71,23 @@ constexpr int SM_BAR = SM_RAW + NRAW * RAW_STRIDE;
 constexpr int SM_X = SM_BAR + 512;                 // row-max exchange between the two softmax warps of a lane quarter
 constexpr int SM_MISC = SM_X + 2 * 4 * 128 * 4;
 constexpr int ATTN_SMEM_BYTES = SM_MISC + 16;
-// warps 0-7 softmax (warp w: TMEM lane quarter w % 4, key half w / 4), 8-15 dequant (two groups of four warps, group g
-// takes units g and g + 2 of every tile), then PV-MMA issue, S-MMA issue and two producers. The warp counts are the measured
+// warps 0-7 softmax (warp w: TMEM lane quarter w % 4, key half w / 4), 8-15 dequant (four groups of two warps, group g
+// takes unit g of every tile: a thread's scale / minimum words then serve eight passes over the record instead of four),
+// then PV-MMA issue, S-MMA issue and two producers. The warp counts are the measured
 // optimum: the kernel is bound by instruction issue, every warp pays a fixed number of hand-off instructions per tile,
 // so fewer, busier dequantising warps win (16 of them: +4 % time), while a single group or four softmax warps leave too
 // little latency hiding (+40 % / +12 %) and sixteen softmax warps pay too many hand-offs (+8 %).
 #ifndef LLATTN_DEQUANT_WARPS
 #define LLATTN_DEQUANT_WARPS 8
 #endif
+#ifndef LLATTN_GROUP_WARPS
+#define LLATTN_GROUP_WARPS 2
+#endif
 #ifndef LLATTN_SOFTMAX_WARPS
 #define LLATTN_SOFTMAX_WARPS 8
 #endif
-constexpr int SOFTMAX_WARPS = LLATTN_SOFTMAX_WARPS, KEY_PARTS = SOFTMAX_WARPS / 4, DEQUANT_WARPS = LLATTN_DEQUANT_WARPS, DEQUANT_GROUPS = DEQUANT_WARPS / 4;
+constexpr int SOFTMAX_WARPS = LLATTN_SOFTMAX_WARPS, KEY_PARTS = SOFTMAX_WARPS / 4, DEQUANT_WARPS = LLATTN_DEQUANT_WARPS, GROUP_WARPS = LLATTN_GROUP_WARPS, DEQUANT_GROUPS = DEQUANT_WARPS / GROUP_WARPS;
+constexpr int GROUP_THREADS = 32 * GROUP_WARPS, DQ_PASSES = 16 / GROUP_WARPS;      // a group converts one record: 32 keys, two per warp and pass
 constexpr int WARP_SERVICE = SOFTMAX_WARPS + DEQUANT_WARPS;
 // Service warps, one per scheduler (a warp runs on scheduler warp % 4 and the softmax warps cannot move): PV issue, S
 // issue and two copy producers that take alternate records, so that no scheduler carries much more than the others.
@@ -99,7 +104,8 @@ enum { B_RAW_FULL = 0, B_RAW_EMPTY = B_RAW_FULL + NRAW, B_K_FULL = B_RAW_EMPTY +
 static_assert(B_COUNT * 8 <= 512, "barrier area");
 static_assert(ATTN_SMEM_BYTES <= 232448, "shared memory budget");
 static_assert(SOFTMAX_WARPS == 4 || SOFTMAX_WARPS == 8 || SOFTMAX_WARPS == 16, "softmax warps: 1, 2 or 4 per TMEM lane quarter");
-static_assert(DEQUANT_GROUPS >= 1 && TILE_UNITS % DEQUANT_GROUPS == 0 && DEQUANT_WARPS % 4 == 0, "dequant warps: groups of four, 1, 2 or 4 groups");
+static_assert((GROUP_WARPS == 2 || GROUP_WARPS == 4) && DEQUANT_WARPS % GROUP_WARPS == 0 && DEQUANT_GROUPS >= 1 && TILE_UNITS % DEQUANT_GROUPS == 0,
+              "dequant warps: groups of two or four, 1, 2 or 4 groups");
 
 struct KParams {
     const SeqDesc* seqs;           // list mode
@@ -201,12 +207,12 @@ __device__ __forceinline__ int tile_off(int key, int c16) {
     return (c16 >> 3) * KBLOCK + key * 128 + (((c16 & 7) ^ (key & 7)) << 4);
 }
 
-// What a dequantising thread knows about itself: warp `wg` of its group of four, half `h16` of the warp, chunk `c16`.
-// K pass p handles key 8p + 2wg + h16, V pass p key 8wg + 2p + h16: either way a warp's load covers two adjacent keys
-// (128 contiguous bytes of codes) and a quarter warp stores one key's row.
+// What a dequantising thread knows about itself: warp `wg` of its group, half `h16` of the warp, chunk `c16`.
+// With G warps in a group, K pass p handles key 2 G p + 2 wg + h16 and V pass p key (32 / G) wg + 2 p + h16: either way
+// a warp's load covers two adjacent keys (128 contiguous bytes of codes) and a quarter warp stores one key's row.
 struct DqThread {
-    int k_src, k_dst;      // pass p adds 512 / 1024
-    int v_src, v_dst;      // pass p adds 128 to v_src; v_dst: (v_dst ^ 32p) + 256p
+    int k_src, k_dst;      // pass p: k_src + 128 G p; (k_dst ^ swizzle flip of odd passes when G = 2) + 256 G p
+    int v_src, v_dst;      // pass p adds 128 to v_src; v_dst: (v_dst ^ 32 (p % 4)) + 256 p
     int c16, wg;
     uint32_t hsel;         // byte-permute selector that broadcasts this thread's half of a word of two fp16
 };
@@ -214,7 +220,7 @@ __device__ __forceinline__ DqThread dq_thread(int dt) {
     DqThread d;
     const int lane = dt & 31, h16 = lane >> 4;
     d.wg = dt >> 5; d.c16 = lane & 15;
-    const int kb = 2 * d.wg + h16, vb = 8 * d.wg + h16;
+    const int kb = 2 * d.wg + h16, vb = (32 / GROUP_WARPS) * d.wg + h16;
     d.k_src = kb * 64 + d.c16 * 4;
     d.k_dst = tile_off(kb, d.c16);
     d.v_src = VOFF + vb * 64 + d.c16 * 4;
@@ -231,36 +237,42 @@ __device__ __forceinline__ void dequant_k(const uint8_t* raw, uint8_t* Kt, const
     const half2* ks = reinterpret_cast<const half2*>(&s4);
     const half2* km = reinterpret_cast<const half2*>(&m4);
 #pragma unroll
-    for (int p = 0; p < 4; ++p) {
+    for (int p = 0; p < DQ_PASSES; ++p) {
         half2 kh[4];
-        unpack8(*reinterpret_cast<const uint32_t*>(raw + d.k_src + p * 512), kh);
+        unpack8(*reinterpret_cast<const uint32_t*>(raw + d.k_src + p * 128 * GROUP_WARPS), kh);
 #pragma unroll
         for (int j = 0; j < 4; ++j) kh[j] = __hfma2(kh[j], ks[j], km[j]);
-        *reinterpret_cast<uint4*>(Kt + d.k_dst + p * 1024) = *reinterpret_cast<const uint4*>(kh);
+        // key 2 G p + kb: with G = 2 the odd passes land 4 keys further, which flips bit 2 of the swizzled chunk position
+        const int flip = GROUP_WARPS == 2 ? 64 * (p & 1) : 0;
+        *reinterpret_cast<uint4*>(Kt + (d.k_dst ^ flip) + p * 256 * GROUP_WARPS) = *reinterpret_cast<const uint4*>(kh);
     }
 }
 // V half: scale and minimum per key; the warp's eight keys' values arrive in one broadcast 16-byte load each.
 __device__ __forceinline__ void dequant_v(const uint8_t* raw, uint8_t* Vt, const DqThread& d) {
-    const uint4 s4 = *reinterpret_cast<const uint4*>(raw + VOFF_META + d.wg * 16);
-    const uint4 m4 = *reinterpret_cast<const uint4*>(raw + VOFF_META + 2 * BLK + d.wg * 16);
-    const uint32_t* sw = reinterpret_cast<const uint32_t*>(&s4);
-    const uint32_t* mw = reinterpret_cast<const uint32_t*>(&m4);
+    uint4 s4[DQ_PASSES / 4], m4[DQ_PASSES / 4];       // scale and minimum of the warp's 32 / G keys
 #pragma unroll
-    for (int p = 0; p < 4; ++p) {
+    for (int k = 0; k < DQ_PASSES / 4; ++k) {
+        s4[k] = *reinterpret_cast<const uint4*>(raw + VOFF_META + (d.wg * (DQ_PASSES / 4) + k) * 16);
+        m4[k] = *reinterpret_cast<const uint4*>(raw + VOFF_META + 2 * BLK + (d.wg * (DQ_PASSES / 4) + k) * 16);
+    }
+    const uint32_t* sw = reinterpret_cast<const uint32_t*>(s4);
+    const uint32_t* mw = reinterpret_cast<const uint32_t*>(m4);
+#pragma unroll
+    for (int p = 0; p < DQ_PASSES; ++p) {
         const uint32_t vsu = __byte_perm(sw[p], sw[p], d.hsel), vmu = __byte_perm(mw[p], mw[p], d.hsel);
         const half2 vs = *reinterpret_cast<const half2*>(&vsu), vm = *reinterpret_cast<const half2*>(&vmu);
         half2 vh[4];
         unpack8(*reinterpret_cast<const uint32_t*>(raw + d.v_src + p * 128), vh);
 #pragma unroll
         for (int j = 0; j < 4; ++j) vh[j] = __hfma2(vh[j], vs, vm);
-        *reinterpret_cast<uint4*>(Vt + (d.v_dst ^ (32 * p)) + 256 * p) = *reinterpret_cast<const uint4*>(vh);
+        *reinterpret_cast<uint4*>(Vt + (d.v_dst ^ (32 * (p & 3))) + 256 * p) = *reinterpret_cast<const uint4*>(vh);
     }
 }
 // The query block's own fp16 K or V (32 keys x 128 channels, row stride NKV * D halves) into a unit of a tile.
 __device__ __forceinline__ void copy_fresh(const half* src, uint8_t* tile_unit, int dt) {
 #pragma unroll
-    for (int k = 0; k < 4; ++k) {
-        const int idx = dt + 128 * k, tok = idx >> 4, c16 = idx & 15;
+    for (int k = 0; k < 512 / GROUP_THREADS; ++k) {
+        const int idx = dt + GROUP_THREADS * k, tok = idx >> 4, c16 = idx & 15;
         *reinterpret_cast<uint4*>(tile_unit + tile_off(tok, c16)) =
             permute8(__ldg(reinterpret_cast<const uint4*>(src + size_t(tok) * NKV * D + c16 * 8)));
     }
@@ -287,7 +299,7 @@ __device__ __forceinline__ void attn_tile_body(const KParams& p, const int cta) 
     }
 
     if (tid == 0) {
-        for (int i = 0; i < NRAW; ++i) { ptx::mbar_init(BAR(B_RAW_FULL + i), 1); ptx::mbar_init(BAR(B_RAW_EMPTY + i), 128); }
+        for (int i = 0; i < NRAW; ++i) { ptx::mbar_init(BAR(B_RAW_FULL + i), 1); ptx::mbar_init(BAR(B_RAW_EMPTY + i), GROUP_THREADS); }
         for (int i = 0; i < 2; ++i) {
             ptx::mbar_init(BAR(B_K_FULL + i), 32 * DEQUANT_WARPS); ptx::mbar_init(BAR(B_V_FULL + i), 32 * DEQUANT_WARPS);
             ptx::mbar_init(BAR(B_K_FREE + i), 1); ptx::mbar_init(BAR(B_PV_DONE + i), 1);
@@ -460,8 +472,8 @@ __device__ __forceinline__ void attn_tile_body(const KParams& p, const int cta) 
         }
     } else if (warp < WARP_SERVICE) {
         // ================================================================== dequant: records -> fp16 operand tiles
-        const int da = tid - 32 * SOFTMAX_WARPS;      // 0..511 over the four groups
-        const int grp = da >> 7, dt = da & 127;       // group g owns unit g of every tile
+        const int da = tid - 32 * SOFTMAX_WARPS;      // over all groups
+        const int grp = da / GROUP_THREADS, dt = da % GROUP_THREADS;       // group g owns units g, g + groups, ... of every tile
         const DqThread dq = dq_thread(dt);
         uint32_t t = 0, r = 0;
         bool alive = true;
