@@ -7,8 +7,8 @@
 //   producer warps: cp.async.bulk of whole records global -> shared ring, completion on an mbarrier (two warps take
 //                   alternate records: one service warp per scheduler keeps the schedulers' loads alike)
 //   dequant warps : nibbles -> fp16 (magic-number unpack, one fp16 FMA per pair as the reference's __hfma2), written
-//                   straight into the no-swizzle UMMA operand layout; fresh fp16 K/V are copied into the same layout
-//   MMA warp      : S = Q K^T  (tcgen05.mma kind::f16, both operands K-major in shared memory, fp32 S in TMEM)
+//                   straight into the 128-byte-swizzle UMMA operand layout; fresh fp16 K/V are copied into the same layout
+//   MMA warps     : S = Q K^T  (tcgen05.mma kind::f16, A = Q in TMEM, B = K K-major in shared memory, fp32 S in TMEM)
 //                   O += P V   (A = P read from TMEM as packed fp16, B = V MN-major in shared memory, fp32 O in TMEM);
 //                   V carries one extra column of ones, so the same MMA also accumulates the softmax row sum from
 //                   exactly the fp16 P the numerator uses (numerator and denominator then share their rounding)
@@ -24,8 +24,7 @@
 // fp16 pairs. K and V tiles live in shared memory in the 128-byte-swizzle layout: a tile is made of blocks of
 // 128 keys x 128 bytes (64 channels of one key per row; K has two blocks, V a third one whose first column is all
 // ones), and the 16-byte chunk c of key k sits at chunk position c ^ (k % 8). K is read K-major (S), V MN-major (PV).
-// Shared-memory bandwidth is what bounds this kernel (tensor-core operand reads plus the dequantisation's loads and
-// stores), so the layout is chosen to make every access of the dequantisation conflict-free: a warp loads the packed
+// The layout is chosen to make every access of the dequantisation conflict-free: a warp loads the packed
 // codes of two whole keys (128 contiguous bytes) and each quarter warp stores the eight 16-byte chunks of one key's
 // row. Within each group of 8 channels the order is (0,4,1,5,2,6,3,7): that is what the shift-free nibble unpack
 // produces, Q and the fresh K are stored in the same order (a dot product does not care) and V's order is undone when
