@@ -10,7 +10,7 @@
 // nodes (:524-552), `attn::kv_commit<<<dim3(4, nb), 128>>>` (:591,:656).
 //
 // What differs from the file it replaces (all visible through the constants below):
-//   ATT_NTH is 640 and SMEM_BYTES about 203 KB (one CTA per SM; the reference ran 128 threads, 79 KB, two per SM);
+//   ATT_NTH is 512 and SMEM_BYTES about 203 KB (one CTA per SM; the reference ran 128 threads, 79 KB, two per SM);
 //   a CTA's chunk should hold a multiple of 4 blocks (128-key MMA tiles) — any blocks_per_chunk is correct, multiples
 //   of 4 are faster; and B200 wants about one chunk per SM and kv head quarter, so a caller after speed sizes its
 //   partial buffers for MAX_CHUNKS_HINT chunks (engine/engine.cu:301 sizes them for 4) and calls pick_bpc below,
@@ -54,12 +54,26 @@ __host__ __device__ inline int chunks_for(int nblocks, int bpc) { return nblocks
 // engine/attn.cu:361-364 asked for ~4 chunks per head (8 SMs). Here: about one chunk per SM over the 4 kv heads and
 // nbatch query blocks, at least 8 blocks per chunk, on a multiple of 4. With max_chunks the caller caps the count to
 // what its partial buffers hold (pass 4 to reproduce the reference's buffer sizing).
+//
+// Buffer bound for an UNMODIFIED engine. The reference sizes Opart/Mpart/Lpart for PB x 4 heads x 4 chunks = 256 slots
+// (PB = 16, engine/engine.cu:301-304) and calls pick_bpc(nblocks, nb) with two arguments (engine.cu:429,535,594). A
+// launch writes slot indices below nb x 4 x nchunks, and nchunks never exceeds the cap below. With the default cap that
+// is 1 x 4 x 37 = 148 slots for a decode step and at most 192 for a prefill pass (nb = 12: 4 chunks, nb = 16: 3 chunks),
+// under 256 for every nb in 1..16; the static_assert keeps it so if either constant changes. An engine with a smaller
+// PB must pass max_chunks = 4.
+constexpr int cmax(int a, int b) { return a > b ? a : b; }
+constexpr int cmin(int a, int b) { return a < b ? a : b; }
+constexpr int chunk_cap(int nbatch, int max_chunks) { return cmax(1, cmin(max_chunks, (148 + 4 * nbatch - 1) / (4 * nbatch))); }
 inline int pick_bpc(int nblocks, int nbatch, int max_chunks = MAX_CHUNKS_HINT) {
-    const int want = std::max(1, std::min(max_chunks, (148 + 4 * nbatch - 1) / (4 * nbatch)));
+    const int want = chunk_cap(nbatch, max_chunks);
     int bpc = std::max(1, (nblocks + want - 1) / want);
     bpc = std::max(bpc, std::min(nblocks, 8));
     return (bpc + 3) / 4 * 4;
 }
+// chunks never exceed the cap (bpc >= ceil(nblocks / cap)), so nb x 4 x cap bounds the slots a launch touches
+constexpr int REFERENCE_PARTIAL_SLOTS = 16 * 4 * 4;       // PB x kv heads x chunks, engine/engine.cu:301-304
+constexpr bool slots_fit_reference(int nb) { return nb > 16 || (nb * 4 * chunk_cap(nb, MAX_CHUNKS_HINT) <= REFERENCE_PARTIAL_SLOTS && slots_fit_reference(nb + 1)); }
+static_assert(slots_fit_reference(1), "the default chunk cap overflows the partial buffers an unmodified engine allocates");
 
 __global__ void __launch_bounds__(ATT_NTH, 1) attn_partial(Args a) {
     llattn::KParams p{};

@@ -207,7 +207,9 @@ int llattn_attention_static(const void* Q, const void* Kf, const void* Vf, const
  * equal the new prompt's leading full blocks are kept) to many sequences over one pool. A page is one committed
  * 32-token block; its record for kv head h of any layer is record `page * 4 + h` of that layer's pool. Sequences that
  * share a prefix of token blocks share its pages; pages of closed sequences stay reusable until their slot is needed
- * (least recently used first). The caller owns the pools and commits the pages reported as not reused. */
+ * (least recently used first). The caller owns the pools, commits the pages reported as not reused and then tells the
+ * manager so (llattn_kvpool_mark_committed): only marked pages are ever reported as reused or kept after their last
+ * holder closes, so a failed open or a sequence closed before its commit leaves nothing behind that looks committed. */
 typedef struct llattn_kvpool llattn_kvpool;
 int llattn_kvpool_create(int npages, llattn_kvpool** out);
 void llattn_kvpool_destroy(llattn_kvpool* pool);
@@ -218,6 +220,10 @@ int llattn_kvpool_open(llattn_kvpool* pool, const int32_t* tokens, int ntokens, 
 /* A decoded block of 32 final token ids becomes the sequence's next page (*reused = 1 if an identical continuation
  * was already committed by another sequence). */
 int llattn_kvpool_append(llattn_kvpool* pool, int32_t seq_id, const int32_t* block_tokens, int32_t* page_out, int32_t* reused);
+/* The records of the sequence's first `nblocks` pages (all of them if nblocks < 0) have been written: from now on
+ * other sequences with the same leading blocks get them as reused. Call it once the commit has been ordered on the
+ * stream that later readers use. */
+int llattn_kvpool_mark_committed(llattn_kvpool* pool, int32_t seq_id, int nblocks);
 int llattn_kvpool_pages(llattn_kvpool* pool, int32_t seq_id, int32_t* pages_out, int cap, int32_t* nblocks);
 int llattn_kvpool_close(llattn_kvpool* pool, int32_t seq_id);
 /* out6 = pages, free, cached (reusable, unreferenced), block hits, block misses, evictions */

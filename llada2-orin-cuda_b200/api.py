@@ -27,7 +27,7 @@ EXPORTS = (
     "llattn_kv_commit_paged", "llattn_qk_norm_rope", "llattn_attn_partial", "llattn_attn_combine", "llattn_create", "llattn_destroy",
     "llattn_plan_create", "llattn_plan_destroy", "llattn_plan_get_stats", "llattn_plan_preview", "llattn_attention",
     "llattn_attention_parts", "llattn_attention_host", "llattn_host_flush", "llattn_device_status",
-    "llattn_dense_w4a8", "llattn_kvpool_create", "llattn_kvpool_destroy", "llattn_kvpool_open", "llattn_kvpool_append", "llattn_kvpool_pages",
+    "llattn_dense_w4a8", "llattn_kvpool_create", "llattn_kvpool_destroy", "llattn_kvpool_open", "llattn_kvpool_append", "llattn_kvpool_pages", "llattn_kvpool_mark_committed",
     "llattn_kvpool_close", "llattn_kvpool_stats", "llattn_attention_static",
 )
 
@@ -99,6 +99,7 @@ def lib() -> ctypes.CDLL:
         L.llattn_kvpool_open.argtypes = [c_void_p, c_void_p, c_int, POINTER(c_int32), POINTER(c_int32), c_void_p, c_int]
         L.llattn_kvpool_append.argtypes = [c_void_p, c_int32, c_void_p, POINTER(c_int32), POINTER(c_int32)]
         L.llattn_kvpool_pages.argtypes = [c_void_p, c_int32, c_void_p, c_int, POINTER(c_int32)]
+        L.llattn_kvpool_mark_committed.argtypes = [c_void_p, c_int32, c_int]
         L.llattn_kvpool_close.argtypes = [c_void_p, c_int32]
         L.llattn_kvpool_stats.argtypes = [c_void_p, c_void_p]
         L.llattn_device_status.argtypes = [c_void_p, c_void_p, POINTER(c_int)]
@@ -342,6 +343,7 @@ class Plan:
 class KvPool:
     """Host-side page manager with prefix reuse (llattn_kvpool_*): pages are committed 32-token blocks, shared by
     sequences with a common prefix of token blocks, recycled least-recently-used once no open sequence holds them.
+    A page is reported as reused, and kept after its last holder closes, only after mark_committed said its records exist.
     Record of (page p, kv head h) in any layer's pool: p * 4 + h."""
 
     def __init__(self, npages: int):
@@ -377,6 +379,10 @@ class KvPool:
         page, reused = c_int32(0), c_int32(0)
         _check(lib().llattn_kvpool_append(self._h, seq_id, tok.ctypes.data, byref(page), byref(reused)))
         return page.value, bool(reused.value)
+
+    def mark_committed(self, seq_id: int, nblocks: int = -1) -> None:
+        """The records of the sequence's first `nblocks` pages (default: all) exist now; only such pages are reused."""
+        _check(lib().llattn_kvpool_mark_committed(self._h, seq_id, nblocks))
 
     def pages(self, seq_id: int):
         import numpy as np

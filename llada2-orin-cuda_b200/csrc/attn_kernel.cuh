@@ -12,11 +12,13 @@
 //                   O += P V   (A = P read from TMEM as packed fp16, B = V MN-major in shared memory, fp32 O in TMEM);
 //                   V carries one extra column of ones, so the same MMA also accumulates the softmax row sum from
 //                   exactly the fp16 P the numerator uses (numerator and denominator then share their rounding)
-//   softmax warps : one thread per query row (TMEM lane); row max, lazy rescale (the reference maximum moves only
-//                   when exceeded by more than 8 in log2 units, engine/attn.cu:237-255), p = 2^(s*scale*log2e - m),
-//                   P stored back over S in TMEM as fp16 pairs (the 32 keys of chunk g at columns 32 g .. 32 g + 15, the
-//                   first half of the S columns they were computed from: a softmax warp overwrites only S columns it
-//                   has itself consumed)
+//   softmax warps : four warps, one thread per query row (TMEM lane), all keys of the row: no exchange between warps.
+//                   One pass per tile: p = 2^(s*scale*log2e - mref) for 16 scores at a time while the next 16 arrive
+//                   from tensor memory, the chunk maximum taken on the way; P goes back over S in TMEM as fp16 pairs
+//                   (the 32 keys of chunk g at columns 32 g .. 32 g + 15, the first half of the S columns they were
+//                   computed from). The reference exponent mref is the exact row maximum of the run's first tile and
+//                   moves only when a later score exceeds it by more than 8 in log2 units (engine/attn.cu:237-255
+//                   rescales lazily in the same way); that rare path rescales O in tensor memory, out of line
 // The run's un-normalised O (fp32), reference maximum (log2 units) and row sum go to a partial slot in the format of
 // the reference's Opart/Mpart/Lpart (engine/attn.cu:291-305); merge_kernel.cuh folds the slots of a tile together.
 //
@@ -42,9 +44,12 @@ namespace llattn {
 #ifdef LLATTN_TRACE
 __device__ unsigned long long* g_trace_buf;      // [warps][LLATTN_TRACE_EVENTS] of (clock << 24 | tile << 8 | event)
 constexpr int LLATTN_TRACE_EVENTS = 2048;
+#ifndef LLATTN_TRACE_ONLY
+#define LLATTN_TRACE_ONLY (ev)          // tuning: keep a single event (less disturbance)
+#endif
 #define LLATTN_TR(ev, tile)                                                                                    \
     do {                                                                                                       \
-        if (trace_ptr && trace_n < LLATTN_TRACE_EVENTS)                                                        \
+        if ((ev) == (LLATTN_TRACE_ONLY) && trace_ptr && trace_n < LLATTN_TRACE_EVENTS)                                                        \
             trace_ptr[trace_n++] =                                 \
                 (static_cast<unsigned long long>(clock64()) << 24) | (static_cast<unsigned long long>((tile) & 0xffff) << 8) | (ev); \
     } while (0)
@@ -52,7 +57,7 @@ constexpr int LLATTN_TRACE_EVENTS = 2048;
 #define LLATTN_TR(ev, tile) do {} while (0)
 #endif
 #ifndef LLATTN_SKIP
-#define LLATTN_SKIP 0      // tuning builds only: bit 0 = no dequantisation, bit 1 = no softmax arithmetic (results are garbage)
+#define LLATTN_SKIP 0      // tuning builds only: bit 0 = no dequantisation, bit 1 = no exponentials (results are garbage)
 #endif
 
 constexpr int TILE_UNITS = 4;
@@ -61,48 +66,53 @@ constexpr int TILE_BYTES = 2 * KBLOCK;             // K tile: channels 0-63, 64-
 constexpr int VTILE_BYTES = 3 * KBLOCK;            // V tile: dims 0-63, 64-127, then the block with the ones column
 constexpr int UNIT_BYTES = 32 * 128;               // a unit's 32 keys inside a block
 constexpr int PV_N = 144;                          // dims 0..127, column 128 = row sum, 129..143 unused
-constexpr int NRAW = 8;                            // records in flight (two tiles' worth)
+#ifndef LLATTN_NRAW
+#define LLATTN_NRAW 8
+#endif
+constexpr int NRAW = LLATTN_NRAW;                  // records in flight (8 = two tiles' worth)
 constexpr int RAW_STRIDE = 4864;                   // 4736 rounded up to a multiple of 128
 constexpr int SM_K = 0;                            // two K tiles (every tile base is 1024-byte aligned)
 constexpr int SM_V = SM_K + 2 * TILE_BYTES;        // two V tiles
 constexpr int SM_RAW = SM_V + 2 * VTILE_BYTES;
 constexpr int SM_BAR = SM_RAW + NRAW * RAW_STRIDE;
-constexpr int SM_X = SM_BAR + 512;                 // row-max exchange between the two softmax warps of a lane quarter
-constexpr int SM_MISC = SM_X + 2 * 4 * 128 * 4;
+constexpr int SM_MISC = SM_BAR + 512;
 constexpr int ATTN_SMEM_BYTES = SM_MISC + 16;
-// warps 0-7 softmax (warp w: TMEM lane quarter w % 4, key half w / 4), 8-15 dequant (four groups of two warps, group g
-// takes unit g of every tile: a thread's scale / minimum words then serve eight passes over the record instead of four),
-// then PV-MMA issue, S-MMA issue and two producers. The warp counts are the measured
-// optimum: the kernel is bound by instruction issue, every warp pays a fixed number of hand-off instructions per tile,
-// so fewer, busier dequantising warps win (16 of them: +4 % time), while a single group or four softmax warps leave too
-// little latency hiding (+40 % / +12 %) and sixteen softmax warps pay too many hand-offs (+8 %).
+// warps 0-3 softmax (warp w: TMEM lanes 32 w .. 32 w + 31, one query row per thread), 4-11 dequant (four groups of two
+// warps, group g takes unit g of every tile: a thread's scale / minimum words then serve eight passes over the record),
+// then the service warps. Every scheduler carries one softmax warp, two dequantising warps and one service warp.
 #ifndef LLATTN_DEQUANT_WARPS
 #define LLATTN_DEQUANT_WARPS 8
 #endif
 #ifndef LLATTN_GROUP_WARPS
 #define LLATTN_GROUP_WARPS 2
 #endif
-#ifndef LLATTN_SOFTMAX_WARPS
-#define LLATTN_SOFTMAX_WARPS 8
+#ifndef LLATTN_SINGLE_ISSUER
+#define LLATTN_SINGLE_ISSUER 0     // 1: one warp issues PV(t) and then S(t+2); the tensor pipe runs one thread's MMAs in order
 #endif
-constexpr int SOFTMAX_WARPS = LLATTN_SOFTMAX_WARPS, KEY_PARTS = SOFTMAX_WARPS / 4, DEQUANT_WARPS = LLATTN_DEQUANT_WARPS, GROUP_WARPS = LLATTN_GROUP_WARPS, DEQUANT_GROUPS = DEQUANT_WARPS / GROUP_WARPS;
+#ifndef LLATTN_WARP_ARRIVE
+#define LLATTN_WARP_ARRIVE 0       // 1: one arrival per softmax warp on the P barrier instead of one per thread
+#endif
+constexpr int SOFTMAX_WARPS = 4, DEQUANT_WARPS = LLATTN_DEQUANT_WARPS, GROUP_WARPS = LLATTN_GROUP_WARPS, DEQUANT_GROUPS = DEQUANT_WARPS / GROUP_WARPS;
 constexpr int GROUP_THREADS = 32 * GROUP_WARPS, DQ_PASSES = 16 / GROUP_WARPS;      // a group converts one record: 32 keys, two per warp and pass
 constexpr int WARP_SERVICE = SOFTMAX_WARPS + DEQUANT_WARPS;
 // Service warps, one per scheduler (a warp runs on scheduler warp % 4 and the softmax warps cannot move): PV issue, S
 // issue and two copy producers that take alternate records, so that no scheduler carries much more than the others.
 constexpr int WARP_MMA_PV = WARP_SERVICE, WARP_MMA = WARP_SERVICE + 1, WARP_PRODUCER = WARP_SERVICE + 2, PRODUCERS = 2;
-constexpr int ATTN_THREADS = 32 * (WARP_SERVICE + 2 + PRODUCERS);  // 640
+constexpr int ATTN_THREADS = 32 * (WARP_SERVICE + 2 + PRODUCERS);  // 512
+constexpr int P_ARRIVALS = LLATTN_WARP_ARRIVE ? SOFTMAX_WARPS : 32 * SOFTMAX_WARPS;
 constexpr int TMEM_COLS = 512;
 constexpr int TM_S = 0, TM_O = 256, TM_L = TM_O + 128, TM_Q = 400;   // S at columns 0 and 128, O at 256..383, row sum at 384, Q at 400..463
+// The reference exponent of a row moves when a score exceeds it by more than this many powers of two, the reference's own
+// threshold (engine/attn.cu:237-255): p = 2^(x - mref), stored as fp16, then stays below 2^8, and a row that a late key
+// dominates gets that key as its new reference (p = 1 for it, no rounding).
 constexpr float RESCALE_SLACK = 8.f;
 
 // barrier indices
 enum { B_RAW_FULL = 0, B_RAW_EMPTY = B_RAW_FULL + NRAW, B_K_FULL = B_RAW_EMPTY + NRAW, B_V_FULL = B_K_FULL + 2,
        B_K_FREE = B_V_FULL + 2, B_PV_DONE = B_K_FREE + 2, B_S_FULL = B_PV_DONE + 2, B_P_FULL = B_S_FULL + 2,
-       B_Q_FULL = B_P_FULL + 2, B_O_FREE, B_SPARE, B_XCHG = B_SPARE + 2, B_COUNT = B_XCHG + 4 };
+       B_Q_FULL = B_P_FULL + 2, B_O_FREE, B_SPARE, B_COUNT = B_SPARE + 2 };
 static_assert(B_COUNT * 8 <= 512, "barrier area");
 static_assert(ATTN_SMEM_BYTES <= 232448, "shared memory budget");
-static_assert(SOFTMAX_WARPS == 4 || SOFTMAX_WARPS == 8 || SOFTMAX_WARPS == 16, "softmax warps: 1, 2 or 4 per TMEM lane quarter");
 static_assert((GROUP_WARPS == 2 || GROUP_WARPS == 4) && DEQUANT_WARPS % GROUP_WARPS == 0 && DEQUANT_GROUPS >= 1 && TILE_UNITS % DEQUANT_GROUPS == 0,
               "dequant warps: groups of two or four, 1, 2 or 4 groups");
 
@@ -201,6 +211,143 @@ __device__ __forceinline__ float max3(float a, float b, float c) {
     return d;
 }
 
+// Maximum of the 32 scores of a chunk (two chains of 3-input maxima).
+__device__ __forceinline__ float rowmax32(const uint32_t (&r)[32]) {
+    float a = max3(__uint_as_float(r[0]), __uint_as_float(r[1]), __uint_as_float(r[2]));
+    float b = max3(__uint_as_float(r[16]), __uint_as_float(r[17]), __uint_as_float(r[18]));
+#pragma unroll
+    for (int j = 3; j < 15; j += 2) {
+        a = max3(a, __uint_as_float(r[j]), __uint_as_float(r[j + 1]));
+        b = max3(b, __uint_as_float(r[16 + j]), __uint_as_float(r[16 + j + 1]));
+    }
+    return max3(max3(a, b, __uint_as_float(r[15])), __uint_as_float(r[31]), __uint_as_float(r[31]));
+}
+// Score pairs J0 .. J1-1 of a chunk -> p = 2^(s * sl2 - mref) as packed fp16 (the multiply-add on two scores at a time).
+template <int J0, int J1>
+__device__ __forceinline__ void exp_pairs(const uint32_t (&r)[32], uint32_t (&pk)[16], unsigned long long sl2x2, unsigned long long nm2) {
+#pragma unroll
+    for (int j = J0; j < J1; ++j) {
+        if (LLATTN_SKIP & 2) { pk[j] = r[2 * j] & 0x03ff03ffu; continue; }
+        float x0, x1;
+        fma2(r[2 * j], r[2 * j + 1], sl2x2, nm2, x0, x1);
+        const half2 h = __floats2half2_rn(ex2(x0), ex2(x1));
+        pk[j] = *reinterpret_cast<const uint32_t*>(&h);
+    }
+}
+
+// Maximum of 16 scores.
+__device__ __forceinline__ float rowmax16(const uint32_t (&r)[16]) {
+    float a = max3(__uint_as_float(r[0]), __uint_as_float(r[1]), __uint_as_float(r[2]));
+    float b = max3(__uint_as_float(r[8]), __uint_as_float(r[9]), __uint_as_float(r[10]));
+#pragma unroll
+    for (int j = 3; j < 7; j += 2) {
+        a = max3(a, __uint_as_float(r[j]), __uint_as_float(r[j + 1]));
+        b = max3(b, __uint_as_float(r[8 + j]), __uint_as_float(r[8 + j + 1]));
+    }
+    return max3(max3(a, b, __uint_as_float(r[7])), __uint_as_float(r[15]), __uint_as_float(r[15]));
+}
+// Score pairs J0 .. J1-1 of 16 scores -> packed fp16 p.
+template <int J0, int J1>
+__device__ __forceinline__ void exp_pairs16(const uint32_t (&r)[16], uint32_t* pk, unsigned long long sl2x2, unsigned long long nm2) {
+#pragma unroll
+    for (int j = J0; j < J1; ++j) {
+        if (LLATTN_SKIP & 2) { pk[j] = r[2 * j] & 0x03ff03ffu; continue; }
+        float x0, x1;
+        fma2(r[2 * j], r[2 * j + 1], sl2x2, nm2, x0, x1);
+        const half2 h = __floats2half2_rn(ex2(x0), ex2(x1));
+        pk[j] = *reinterpret_cast<const uint32_t*>(&h);
+    }
+}
+
+// p = 2^(s * scale * log2e - mref) must stay below the fp16 maximum. Rows whose chunk maximum `cs` is more than
+// RESCALE_SLACK above their reference (`over`) move the reference to that maximum; what was accumulated under the old
+// reference - O and the row sum of earlier tiles (`have_acc`), and the `chunks_done` chunks of this tile already turned
+// into P - is rescaled. Warp-uniform call, rare (a key 2^8 times heavier than everything before it in the run), kept out
+// of line so that the common path stays small.
+// tlane: tensor-memory address of the warp's lanes at column 0; ts: the tile's S / P buffer; bar_pv, par_pv: barrier and
+// parity of "PV of the previous tile has completed". Returns the row's new reference, NaN when that wait ran out.
+__device__ __noinline__ float raise_reference(float mref, float cs, bool over, int chunks_done, bool have_acc, uint32_t tlane,
+                                              uint32_t ts, uint32_t bar_pv, uint32_t par_pv, volatile int* abort_flag) {
+    const float mnew = over ? cs : mref;
+    const float corr = over ? ex2(mref - mnew) : 1.f;      // 0 for a row that had no reference yet
+    if (have_acc) {
+        if (!ptx::mbar_wait(bar_pv, par_pv, abort_flag)) return __int_as_float(0x7fc00000);
+        ptx::tc_fence_after();
+#pragma unroll 1
+        for (int oc = 0; oc < 4; ++oc) {
+            uint32_t r[32];
+            ptx::tmem_ld32(tlane + TM_O + 32 * oc, r);
+            ptx::tmem_wait_ld_tied(r);
+#pragma unroll
+            for (int j = 0; j < 32; ++j) r[j] = __float_as_uint(__uint_as_float(r[j]) * corr);
+            ptx::tmem_st32(tlane + TM_O + 32 * oc, r);
+        }
+        uint32_t r[16];
+        ptx::tmem_ld16(tlane + TM_L, r);
+        ptx::tmem_wait_ld_tied(r);
+        r[0] = __float_as_uint(__uint_as_float(r[0]) * corr);
+        ptx::tmem_st16(tlane + TM_L, r);
+    }
+    const half2 ch = __float2half2_rn(corr);
+#pragma unroll 1
+    for (int pc = 0; pc < chunks_done; ++pc) {
+        uint32_t r[16];
+        ptx::tmem_ld16(ts + 32 * pc, r);
+        ptx::tmem_wait_ld_tied(r);
+#pragma unroll
+        for (int j = 0; j < 16; ++j) {
+            const half2 h = __hmul2(*reinterpret_cast<const half2*>(&r[j]), ch);
+            r[j] = *reinterpret_cast<const uint32_t*>(&h);
+        }
+        ptx::tmem_st16(ts + 32 * pc, r);
+    }
+    ptx::tmem_wait_st();
+    return mnew;
+}
+
+// One tile of NU 32-key chunks for one query row: S -> P in a single pass, branch-free except for the vote that guards
+// the rare path. Scores arrive 16 columns at a time; the second half of the next chunk is requested once the first half
+// of the current one has been consumed, its maximum is taken between the last exponentials of the current chunk, and P
+// goes back over the first 16 of the 32 S columns it came from. Before the last chunk's exponentials the barrier of the
+// next tile's S is tested (next_bar != 0), so that the test's latency is covered and the next tile starts without a wait
+// when its S is already there. Returns false when a wait of the rare path ran out.
+template <int NU>
+__device__ __forceinline__ bool softmax_tile(float& mref, float sl2, unsigned long long sl2x2, uint32_t tlane, uint32_t ts, bool have_acc,
+                                             uint32_t bar_pv, uint32_t par_pv, volatile int* abort_flag, uint32_t next_bar, uint32_t next_par,
+                                             bool& next_ready) {
+    unsigned long long nm2 = dup2(-mref);
+    uint32_t a0[16], a1[16], b0[16], b1[16];
+    ptx::tmem_ld16(ts, a0);
+    ptx::tmem_ld16(ts + 16, a1);
+    ptx::tmem_wait_ld_tied(a0, a1);
+    float cm = fmaxf(rowmax16(a0), rowmax16(a1));
+#pragma unroll
+    for (int c = 0; c < NU; ++c) {
+        uint32_t (&c0)[16] = (c & 1) ? b0 : a0;
+        uint32_t (&c1)[16] = (c & 1) ? b1 : a1;
+        uint32_t (&n0)[16] = (c & 1) ? a0 : b0;
+        uint32_t (&n1)[16] = (c & 1) ? a1 : b1;
+        const float cs = cm * sl2;
+        const bool over = cs > mref + RESCALE_SLACK;
+        if (__any_sync(0xffffffffu, over)) {
+            mref = raise_reference(mref, cs, over, c, have_acc, tlane, ts, bar_pv, par_pv, abort_flag);
+            if (__any_sync(0xffffffffu, mref != mref)) return false;
+            nm2 = dup2(-mref);
+        }
+        uint32_t pk[16];
+        if (c + 1 < NU) ptx::tmem_ld16(ts + 32 * (c + 1), n0);
+        else next_ready = next_bar != 0 && ptx::mbar_try_wait(next_bar, next_par);
+        exp_pairs16<0, 8>(c0, pk, sl2x2, nm2);
+        ptx::tmem_st8(ts + 32 * c, pk);
+        if (c + 1 < NU) ptx::tmem_ld16(ts + 32 * (c + 1) + 16, n1);
+        exp_pairs16<0, 5>(c1, pk + 8, sl2x2, nm2);
+        if (c + 1 < NU) { ptx::tmem_wait_ld_tied(n0, n1); cm = fmaxf(rowmax16(n0), rowmax16(n1)); }
+        exp_pairs16<5, 8>(c1, pk + 8, sl2x2, nm2);
+        ptx::tmem_st8(ts + 32 * c + 8, pk + 8);
+    }
+    return true;
+}
+
 // Byte offset of (key, 16-byte chunk c16 of its 128 channels) inside a K or V tile.
 __device__ __forceinline__ int tile_off(int key, int c16) {
     return (c16 >> 3) * KBLOCK + key * 128 + (((c16 & 7) ^ (key & 7)) << 4);
@@ -235,10 +382,15 @@ __device__ __forceinline__ void dequant_k(const uint8_t* raw, uint8_t* Kt, const
     const uint4 m4 = permute8(*reinterpret_cast<const uint4*>(raw + KOFF_META + 256 + d.c16 * 16));
     const half2* ks = reinterpret_cast<const half2*>(&s4);
     const half2* km = reinterpret_cast<const half2*>(&m4);
+    // every code word of the thread first: the compiler cannot tell the record ring from the operand tile, so a load
+    // written after a store would wait for it, and each pass would pay the full shared-memory latency
+    uint32_t w[DQ_PASSES];
+#pragma unroll
+    for (int p = 0; p < DQ_PASSES; ++p) w[p] = *reinterpret_cast<const uint32_t*>(raw + d.k_src + p * 128 * GROUP_WARPS);
 #pragma unroll
     for (int p = 0; p < DQ_PASSES; ++p) {
         half2 kh[4];
-        unpack8(*reinterpret_cast<const uint32_t*>(raw + d.k_src + p * 128 * GROUP_WARPS), kh);
+        unpack8(w[p], kh);
 #pragma unroll
         for (int j = 0; j < 4; ++j) kh[j] = __hfma2(kh[j], ks[j], km[j]);
         // key 2 G p + kb: with G = 2 the odd passes land 4 keys further, which flips bit 2 of the swizzled chunk position
@@ -256,12 +408,15 @@ __device__ __forceinline__ void dequant_v(const uint8_t* raw, uint8_t* Vt, const
     }
     const uint32_t* sw = reinterpret_cast<const uint32_t*>(s4);
     const uint32_t* mw = reinterpret_cast<const uint32_t*>(m4);
+    uint32_t w[DQ_PASSES];
+#pragma unroll
+    for (int p = 0; p < DQ_PASSES; ++p) w[p] = *reinterpret_cast<const uint32_t*>(raw + d.v_src + p * 128);
 #pragma unroll
     for (int p = 0; p < DQ_PASSES; ++p) {
         const uint32_t vsu = __byte_perm(sw[p], sw[p], d.hsel), vmu = __byte_perm(mw[p], mw[p], d.hsel);
         const half2 vs = *reinterpret_cast<const half2*>(&vsu), vm = *reinterpret_cast<const half2*>(&vmu);
         half2 vh[4];
-        unpack8(*reinterpret_cast<const uint32_t*>(raw + d.v_src + p * 128), vh);
+        unpack8(w[p], vh);
 #pragma unroll
         for (int j = 0; j < 4; ++j) vh[j] = __hfma2(vh[j], vs, vm);
         *reinterpret_cast<uint4*>(Vt + (d.v_dst ^ (32 * (p & 3))) + 256 * p) = *reinterpret_cast<const uint4*>(vh);
@@ -302,12 +457,11 @@ __device__ __forceinline__ void attn_tile_body(const KParams& p, const int cta) 
         for (int i = 0; i < 2; ++i) {
             ptx::mbar_init(BAR(B_K_FULL + i), 32 * DEQUANT_WARPS); ptx::mbar_init(BAR(B_V_FULL + i), 32 * DEQUANT_WARPS);
             ptx::mbar_init(BAR(B_K_FREE + i), 1); ptx::mbar_init(BAR(B_PV_DONE + i), 1);
-            ptx::mbar_init(BAR(B_S_FULL + i), 1); ptx::mbar_init(BAR(B_P_FULL + i), 32 * SOFTMAX_WARPS);
+            ptx::mbar_init(BAR(B_S_FULL + i), 1); ptx::mbar_init(BAR(B_P_FULL + i), P_ARRIVALS);
         }
         ptx::mbar_init(BAR(B_Q_FULL), 32 * SOFTMAX_WARPS); ptx::mbar_init(BAR(B_O_FREE), 32 * SOFTMAX_WARPS);
         ptx::mbar_init(BAR(B_SPARE), 1);
         ptx::mbar_init(BAR(B_SPARE + 1), 1);
-        for (int i = 0; i < 4; ++i) ptx::mbar_init(BAR(B_XCHG + i), 32 * KEY_PARTS);
         ptx::fence_mbar_init();
         *abort_flag = 0;
     }
@@ -325,13 +479,13 @@ __device__ __forceinline__ void attn_tile_body(const KParams& p, const int cta) 
 
     if (warp < SOFTMAX_WARPS) {
         // ================================================================== softmax + epilogue
-        // thread = (query row, key part): the KEY_PARTS warps of a TMEM lane quarter split a tile's four 32-key chunks
-        // (chunk g = S columns [32 g, 32 g + 32); its P goes to the first 16 of the same columns, so a warp only ever
-        // overwrites S it has itself consumed), the channels of Q and the columns of O
-        constexpr int CPW = 4 / KEY_PARTS;            // chunks per warp and tile = 32-column groups of O per warp
-        const int q = warp & 3, kp = warp >> 2, row = q * 32 + lane;
-        const uint32_t tlane = tmem + (uint32_t(q * 32) << 16);
-        float* xb = reinterpret_cast<float*>(smem + SM_X);
+        // thread = query row = TMEM lane (warp w owns lanes 32 w .. 32 w + 31): it sees all keys of its row, so the row
+        // maximum needs no exchange with other warps. One pass per tile: a 32-key chunk of S is loaded while the previous
+        // chunk's exponentials run, its maximum is taken between them, and P goes back over the first 16 of the S columns
+        // it came from.
+        const int row = warp * 32 + lane;
+        const uint32_t tlane = tmem + (uint32_t(warp * 32) << 16);
+        const unsigned long long sl2x2 = dup2(p.sl2);
         uint32_t t = 0;
         bool alive = true;
 #pragma unroll 1
@@ -339,116 +493,77 @@ __device__ __forceinline__ void attn_tile_body(const KParams& p, const int cta) 
             WorkItem w; SeqDesc s;
             if (!fetch_item(p, ii, w, s)) continue;
             const int U = w.rec_count + w.fresh, ntiles = (U + TILE_UNITS - 1) / TILE_UNITS;
+            // Reference exponent of the row, log2 units: the exact maximum of the run's first tile (a row dominated by a
+            // key of that tile then has p = 1 for it, without rounding); it moves only when a later score exceeds it by
+            // more than RESCALE_SLACK (engine/attn.cu:237-255 moves its reference lazily in the same way).
             float mref = -INFINITY;
-            {   // this thread's query row, channels [32 CPW kp, 32 CPW (kp + 1)), into tensor memory as fp16 pairs. Every S
-                // MMA of the previous item has completed: this warp has seen the S of its last tile.
-                const half* src = p.Q + ((size_t(s.q_first + w.qblk) * BLK + (row >> 2)) * NQH + 4 * w.kvh + (row & 3)) * D + 32 * CPW * kp;
+            bool s_ready = false;              // the tile's S has been seen complete already (tested during the previous tile)
+            {   // this thread's query row into tensor memory as fp16 pairs. Every S MMA of the previous item has completed:
+                // this warp has seen the S of its last tile.
+                const half* src = p.Q + ((size_t(s.q_first + w.qblk) * BLK + (row >> 2)) * NQH + 4 * w.kvh + (row & 3)) * D;
 #pragma unroll 1
-                for (int c = 0; c < CPW; ++c) {
+                for (int c = 0; c < 4; ++c) {
                     uint32_t r[16];
 #pragma unroll
                     for (int g = 0; g < 4; ++g) {
                         const uint4 v = permute8(__ldg(reinterpret_cast<const uint4*>(src + 32 * c + 8 * g)));
                         r[4 * g] = v.x; r[4 * g + 1] = v.y; r[4 * g + 2] = v.z; r[4 * g + 3] = v.w;
                     }
-                    ptx::tmem_st16(tlane + TM_Q + 16 * (CPW * kp + c), r);
+                    ptx::tmem_st16(tlane + TM_Q + 16 * c, r);
                 }
                 ptx::tmem_wait_st();
                 ptx::tc_fence_before();
                 ptx::mbar_arrive(BAR(B_Q_FULL));
             }
 #pragma unroll 1
-            for (int i = 0; i < ntiles; ++i, ++t) {
+            for (int i = 0; i < ntiles && alive; ++i, ++t) {
                 const int b = t & 1, nu = min(TILE_UNITS, U - TILE_UNITS * i);
-                const int nc = max(0, min(CPW, nu - CPW * kp));          // 32-key chunks of this tile this warp owns
                 LLATTN_TR(1, t);
-                if (!ptx::mbar_wait(BAR(B_S_FULL + b), (t >> 1) & 1, abort_flag)) { alive = false; errbits |= ERR_WAIT_SOFTMAX; break; }
+                if (!s_ready && !ptx::mbar_wait(BAR(B_S_FULL + b), (t >> 1) & 1, abort_flag)) { alive = false; errbits |= ERR_WAIT_SOFTMAX; break; }
                 LLATTN_TR(2, t);
                 ptx::tc_fence_after();
-                const uint32_t ts = tlane + TM_S + b * 128 + 32 * CPW * kp;
-                float mx = -INFINITY;
+                const uint32_t ts = tlane + TM_S + b * 128, bar_pv = BAR(B_PV_DONE + (b ^ 1)), par_pv = ((t - 1) >> 1) & 1;
+                // the next tile's S (other buffer) is tested for during this tile's last chunk, except across runs
+                const uint32_t next_bar = i + 1 < ntiles ? BAR(B_S_FULL + (b ^ 1)) : 0u, next_par = ((t + 1) >> 1) & 1;
+                if (i == 0) {
+                    float mx = -INFINITY;
 #pragma unroll 1
-                for (int c = 0; c < nc; ++c) {
-                    uint32_t r[32];
-                    ptx::tmem_ld32(ts + 32 * c, r);
-                    ptx::tmem_wait_ld();
-#pragma unroll
-                    for (int j = 0; j < 32; j += 2) {
-                        if (LLATTN_SKIP & 2) { if (j == 0) mx = fmaxf(mx, __uint_as_float(r[0])); }
-                        else mx = max3(mx, __uint_as_float(r[j]), __uint_as_float(r[j + 1]));
-                    }
-                }
-                // row max over all parts: exchange through shared memory with the other warps of the lane quarter
-                // (double-buffered by tile parity; the quarter's mbarrier, one phase per tile, orders write -> read and
-                // its wait is bounded)
-                LLATTN_TR(5, t);
-                if (KEY_PARTS > 1) {
-                    xb[b * 512 + kp * 128 + row] = mx;
-                    ptx::mbar_arrive(BAR(B_XCHG + q));
-                    if (!ptx::mbar_wait(BAR(B_XCHG + q), t & 1, abort_flag)) { alive = false; errbits |= ERR_WAIT_SOFTMAX; break; }
-#pragma unroll
-                    for (int k = 1; k < KEY_PARTS; ++k) mx = fmaxf(mx, xb[b * 512 + ((kp + k) % KEY_PARTS) * 128 + row]);
-                }
-                LLATTN_TR(3, t);
-                const float msc = mx * p.sl2;
-                const bool moved = msc > mref + RESCALE_SLACK;
-                if (i > 0 && __any_sync(0xffffffffu, moved)) {
-                    // the accumulated O of these rows is rescaled to the new reference maximum (this warp's share of the
-                    // columns); every PV issued so far must have landed first
-                    if (!ptx::mbar_wait(BAR(B_PV_DONE + (b ^ 1)), ((t - 1) >> 1) & 1, abort_flag)) { alive = false; errbits |= ERR_WAIT_SOFTMAX; break; }
-                    ptx::tc_fence_after();
-                    const float corr = moved ? ex2(mref - msc) : 1.f;
-#pragma unroll 1
-                    for (int c = 0; c < CPW; ++c) {
+                    for (int c = 0; c < nu; ++c) {
                         uint32_t r[32];
-                        ptx::tmem_ld32(tlane + TM_O + 32 * (CPW * kp + c), r);
-                        ptx::tmem_wait_ld();
-#pragma unroll
-                        for (int j = 0; j < 32; ++j) r[j] = __float_as_uint(__uint_as_float(r[j]) * corr);
-                        ptx::tmem_st32(tlane + TM_O + 32 * (CPW * kp + c), r);
+                        ptx::tmem_ld32(ts + 32 * c, r);
+                        ptx::tmem_wait_ld_tied(r);
+                        mx = fmaxf(mx, rowmax32(r));
                     }
-                    if (kp == KEY_PARTS - 1) {
-                        uint32_t r[16];
-                        ptx::tmem_ld16(tlane + TM_L, r);
-                        ptx::tmem_wait_ld();
-                        r[0] = __float_as_uint(__uint_as_float(r[0]) * corr);
-                        ptx::tmem_st16(tlane + TM_L, r);
-                    }
-                    ptx::tmem_wait_st();
+                    mref = mx * p.sl2;
                 }
-                if (moved) mref = msc;
-                const unsigned long long sl2x2 = dup2(p.sl2), nmx2 = dup2(-mref);
-#pragma unroll 1
-                for (int c = 0; c < nc; ++c) {
-                    uint32_t r[32], pk[16];
-                    ptx::tmem_ld32(ts + 32 * c, r);
-                    ptx::tmem_wait_ld();
-#pragma unroll
-                    for (int j = 0; j < 16; ++j) {
-                        if (LLATTN_SKIP & 2) { pk[j] = r[2 * j] & 0x03ff03ffu; continue; }
-                        float x0, x1;
-                        fma2(r[2 * j], r[2 * j + 1], sl2x2, nmx2, x0, x1);
-                        const half2 h = __floats2half2_rn(ex2(x0), ex2(x1));
-                        pk[j] = *reinterpret_cast<const uint32_t*>(&h);
-                    }
-                    ptx::tmem_st16(ts + 32 * c, pk);      // P chunk over the S columns it was computed from
-                }
+                bool ok;
+                if (nu == TILE_UNITS) ok = softmax_tile<TILE_UNITS>(mref, p.sl2, sl2x2, tlane, ts, i > 0, bar_pv, par_pv, abort_flag, next_bar, next_par, s_ready);      // every tile of a run but its last
+                else if (nu == 3) ok = softmax_tile<3>(mref, p.sl2, sl2x2, tlane, ts, i > 0, bar_pv, par_pv, abort_flag, next_bar, next_par, s_ready);
+                else if (nu == 2) ok = softmax_tile<2>(mref, p.sl2, sl2x2, tlane, ts, i > 0, bar_pv, par_pv, abort_flag, next_bar, next_par, s_ready);
+                else ok = softmax_tile<1>(mref, p.sl2, sl2x2, tlane, ts, i > 0, bar_pv, par_pv, abort_flag, next_bar, next_par, s_ready);
+                if (!ok) { alive = false; errbits |= ERR_WAIT_SOFTMAX; }
+                if (!alive) break;
                 ptx::tmem_wait_st();
                 ptx::tc_fence_before();
+#if LLATTN_WARP_ARRIVE
+                __syncwarp();
+                if (lane == 0) ptx::mbar_arrive(BAR(B_P_FULL + b));
+#else
                 ptx::mbar_arrive(BAR(B_P_FULL + b));
+#endif
                 LLATTN_TR(4, t);
             }
             if (!alive) break;
-            // ---- epilogue: un-normalised O (this warp's share of the columns), reference maximum and row sum of the run
+            // ---- epilogue: un-normalised O, reference exponent and row sum of the run
             const uint32_t tl = t - 1;
             if (!ptx::mbar_wait(BAR(B_PV_DONE + (tl & 1)), (tl >> 1) & 1, abort_flag)) { alive = false; errbits |= ERR_WAIT_SOFTMAX; break; }
             ptx::tc_fence_after();
-            float* orow = p.Opart + (size_t(w.slot) * QR + row) * D + 32 * CPW * kp;
+            float* orow = p.Opart + (size_t(w.slot) * QR + row) * D;
 #pragma unroll 1
-            for (int c = 0; c < CPW; ++c) {
+            for (int c = 0; c < 4; ++c) {
                 uint32_t r[32];
-                ptx::tmem_ld32(tlane + TM_O + 32 * (CPW * kp + c), r);
-                ptx::tmem_wait_ld();
+                ptx::tmem_ld32(tlane + TM_O + 32 * c, r);
+                ptx::tmem_wait_ld_tied(r);
 #pragma unroll
                 for (int g = 0; g < 4; ++g) {      // positions (0..7) hold dims (0,4,1,5,2,6,3,7)
                     const float4 lo = make_float4(__uint_as_float(r[8 * g]), __uint_as_float(r[8 * g + 2]),
@@ -459,13 +574,13 @@ __device__ __forceinline__ void attn_tile_body(const KParams& p, const int cta) 
                     *reinterpret_cast<float4*>(orow + 32 * c + 8 * g + 4) = hi;
                 }
             }
-            if (kp == KEY_PARTS - 1) {
+            {
                 uint32_t r[16];
                 ptx::tmem_ld16(tlane + TM_L, r);
-                ptx::tmem_wait_ld();
+                ptx::tmem_wait_ld_tied(r);
                 p.Lpart[size_t(w.slot) * QR + row] = __uint_as_float(r[0]);
             }
-            if (kp == 0) p.Mpart[size_t(w.slot) * QR + row] = mref;
+            p.Mpart[size_t(w.slot) * QR + row] = mref;
             ptx::tc_fence_before();
             ptx::mbar_arrive(BAR(B_O_FREE));
         }
@@ -608,8 +723,7 @@ __device__ __forceinline__ void attn_tile_body(const KParams& p, const int cta) 
             }
         }
     } else if (warp == WARP_MMA) {
-        // ================================================================== S = Q K^T issue (one elected lane issues, the warp stays together)
-        // Two issuing warps (this one and the PV one below) halve the per-tile instruction chain on the critical path.
+        // ================================================================== MMA issue (one elected lane issues, the warp stays together)
         // Loop bounds, tile counts and wait results are made visibly warp-uniform so that the operands of the MMAs can
         // live in uniform registers.
         uint32_t t = 0, itc = 0;
@@ -619,6 +733,61 @@ __device__ __forceinline__ void attn_tile_body(const KParams& p, const int cta) 
         const uint32_t klo0 = ptx::desc_lo(k_s, 16), klo1 = ptx::desc_lo(k_s + TILE_BYTES, 16), khi = ptx::desc_hi(1024) | (2u << 29);
         const uint32_t tmem = uniform_u32(tmem_any);
         const int i0 = uniform_i32(i0_any), i1 = uniform_i32(i1_any);
+#if LLATTN_SINGLE_ISSUER
+        // This warp issues everything, per tile t in the order PV(t), S(t+2). S(t+2) overwrites the buffer that holds P(t);
+        // the tensor pipe executes the MMAs of one thread in issue order, so no wait for PV(t) to complete is needed.
+        const uint32_t v_s = ptx::smem_u32(smem + SM_V);
+        const uint32_t idO = ptx::idesc_f16(128, PV_N, false, true);
+        const uint32_t vlo0 = ptx::desc_lo(v_s, KBLOCK), vlo1 = ptx::desc_lo(v_s + VTILE_BYTES, KBLOCK), vhi = ptx::desc_hi(1024) | (2u << 29);
+        auto issue_s = [&](uint32_t tt, int nu) -> bool {
+            const uint32_t b = tt & 1;
+            if (!uniform_i32(ptx::mbar_wait(BAR(B_K_FULL + b), (tt >> 1) & 1, abort_flag))) return false;
+            ptx::tc_fence_after();
+            const uint32_t idS = ptx::idesc_f16(128, 32 * nu, false, false);
+            ptx::mma_ts_s8_warp<KBLOCK / 16>(tmem + TM_S + b * 128, tmem + TM_Q, b ? klo1 : klo0, khi, idS, BAR(B_S_FULL + b), BAR(B_K_FREE + b));
+            return true;
+        };
+#pragma unroll 1
+        for (int ii = i0; ii < i1 && alive; ++ii) {
+            WorkItem w; SeqDesc s;
+            if (!uniform_i32(fetch_item(p, ii, w, s))) continue;
+            const int U = uniform_i32(w.rec_count + w.fresh), ntiles = (U + TILE_UNITS - 1) / TILE_UNITS;
+            if (!uniform_i32(ptx::mbar_wait(BAR(B_Q_FULL), itc & 1, abort_flag))) { alive = false; errbits |= ERR_WAIT_MMA; break; }
+            for (int j = 0; j < 2 && j < ntiles && alive; ++j)
+                if (!issue_s(t + j, min(TILE_UNITS, U - TILE_UNITS * j))) { alive = false; errbits |= ERR_WAIT_MMA; }
+#pragma unroll 1
+            for (int i = 0; i < ntiles && alive; ++i, ++t) {
+                const uint32_t b = t & 1;
+                const int nu = min(TILE_UNITS, U - TILE_UNITS * i);
+                LLATTN_TR(22, t);
+                if (!uniform_i32(ptx::mbar_wait(BAR(B_V_FULL + b), (t >> 1) & 1, abort_flag))) { alive = false; errbits |= ERR_WAIT_MMA; break; }
+                if (!uniform_i32(ptx::mbar_wait(BAR(B_P_FULL + b), (t >> 1) & 1, abort_flag))) { alive = false; errbits |= ERR_WAIT_MMA; break; }
+                LLATTN_TR(24, t);
+                // the previous item's epilogue must have read O before the first PV of this item overwrites it
+                if (i == 0 && itc > 0 && !uniform_i32(ptx::mbar_wait(BAR(B_O_FREE), (itc - 1) & 1, abort_flag))) { alive = false; errbits |= ERR_WAIT_MMA; break; }
+                ptx::tc_fence_after();
+                {
+                    const uint32_t pb = tmem + TM_S + b * 128, vlo = b ? vlo1 : vlo0;
+                    if (nu == TILE_UNITS) {
+                        ptx::mma_ts_pv8_warp(tmem + TM_O, pb, vlo, vhi, idO, i == 0 ? 0u : 1u, BAR(B_PV_DONE + b));
+                    } else {
+#pragma unroll
+                        for (int u = 0; u < TILE_UNITS - 1; ++u)
+                            if (u < nu) {
+                                const uint64_t d0 = (uint64_t(vhi) << 32) | (vlo + 256u * u);
+                                ptx::mma_ts_x2_warp(tmem + TM_O, pb + 32 * u, d0, d0 + 128, idO, (i == 0 && u == 0) ? 0u : 1u);
+                            }
+                        ptx::mma_commit_warp(BAR(B_PV_DONE + b));
+                    }
+                }
+                LLATTN_TR(26, t);
+                if (i + 2 < ntiles && !issue_s(t + 2, min(TILE_UNITS, U - TILE_UNITS * (i + 2)))) { alive = false; errbits |= ERR_WAIT_MMA; break; }
+                LLATTN_TR(25, t);
+            }
+            ++itc;
+        }
+#else
+        // S = Q K^T issue; the PV warp below issues O += P V. Two issuing warps halve the per-tile instruction chain.
 #pragma unroll 1
         for (int ii = i0; ii < i1 && alive; ++ii) {
             WorkItem w; SeqDesc s;
@@ -643,6 +812,7 @@ __device__ __forceinline__ void attn_tile_body(const KParams& p, const int cta) 
             }
             ++itc;
         }
+#endif
         // every MMA issued must have retired before tensor memory is released
         ptx::mma_commit_warp(BAR(B_SPARE));
         {
@@ -650,6 +820,7 @@ __device__ __forceinline__ void attn_tile_body(const KParams& p, const int cta) 
             if (!ptx::mbar_wait(BAR(B_SPARE), 0, &never)) errbits |= ERR_WAIT_TEARDOWN;
         }
     } else {
+#if !LLATTN_SINGLE_ISSUER
         // ================================================================== O += P V issue
         uint32_t t = 0, itc = 0;
         bool alive = true;
@@ -700,6 +871,7 @@ __device__ __forceinline__ void attn_tile_body(const KParams& p, const int cta) 
             volatile int never = 0;
             if (!ptx::mbar_wait(BAR(B_SPARE + 1), 0, &never)) errbits |= ERR_WAIT_TEARDOWN;
         }
+#endif
     }
 
     if (errbits && p.err) atomicOr(p.err, errbits);

@@ -6,6 +6,11 @@
 // page * 4 + head of each layer's pool); a page is identified by the chain of token blocks that leads to it, so two
 // requests that share a prefix share its pages. Pages of closed sequences stay cached until their slot is needed
 // (least recently used first). No CUDA call is made here: the caller owns the pools and runs the commits.
+//
+// A page counts as reusable only once its records exist: the caller says so with llattn_kvpool_mark_committed after the
+// commit kernel has been ordered. Until then a second sequence with the same prefix gets the same page index (it would
+// write the same bytes) but is told the block is NOT reused, so it prefills it too; and a page that loses its last
+// holder before it was marked goes back to the free list instead of the cache.
 
 #include <list>
 #include <unordered_map>
@@ -17,7 +22,8 @@ struct KvPage {
     int32_t parent = -1;              // page of the previous block in the chain (-1 for block 0)
     int32_t refs = 0;                 // open sequences that hold it
     int32_t tokens[32];
-    bool cached = false;              // refs == 0 and still registered: in the LRU list
+    bool committed = false;           // its records have been written (llattn_kvpool_mark_committed)
+    bool cached = false;              // refs == 0, committed and still registered: in the LRU list
     std::list<int32_t>::iterator lru;
 };
 
@@ -67,8 +73,12 @@ struct llattn_kvpool {
     void drop(int32_t p) {
         KvPage& pg = pages[p];
         if (--pg.refs == 0) {
-            if (pg.key) { pg.lru = lru.insert(lru.end(), p); pg.cached = true; }
-            else free_list.push_back(p);
+            if (pg.key && pg.committed) { pg.lru = lru.insert(lru.end(), p); pg.cached = true; }
+            else {                                            // never committed: nothing worth keeping
+                if (pg.key) unregister(p);
+                pg.committed = false;
+                free_list.push_back(p);
+            }
         }
     }
     // A page nobody holds: a free one, else the least recently used cached one. A cached page whose children are
@@ -79,6 +89,7 @@ struct llattn_kvpool {
         const int32_t p = lru.front();
         lru.pop_front();
         pages[p].cached = false;
+        pages[p].committed = false;
         unregister(p);
         ++evictions;
         return p;
@@ -86,12 +97,17 @@ struct llattn_kvpool {
     int32_t add_block(uint64_t parent_key, int32_t parent, const int32_t* tok, bool* reused) {
         const uint64_t key = kv_block_key(parent_key, tok);
         int32_t p = find(key, parent, tok);
-        if (p >= 0) { *reused = true; take(p); ++hits; return p; }
+        if (p >= 0) {                                         // same chain of blocks: same page; reused only if its records exist
+            *reused = pages[p].committed;
+            take(p);
+            if (*reused) ++hits; else ++misses;
+            return p;
+        }
         *reused = false;
         p = grab();
         if (p < 0) return -1;
         KvPage& pg = pages[p];
-        pg.key = key; pg.parent = parent; pg.refs = 0;
+        pg.key = key; pg.parent = parent; pg.refs = 0; pg.committed = false;
         memcpy(pg.tokens, tok, sizeof(pg.tokens));
         by_key.emplace(key, p);
         take(p);
@@ -162,6 +178,18 @@ int llattn_kvpool_append(llattn_kvpool* kp, int32_t seq_id, const int32_t* block
     mine.push_back(p);
     *page_out = p;
     if (reused) *reused = hit ? 1 : 0;
+    return LLATTN_OK;
+}
+
+int llattn_kvpool_mark_committed(llattn_kvpool* kp, int32_t seq_id, int nblocks) {
+    if (!kp) return fail(LLATTN_EINVAL, "kvpool_mark_committed: null pool");
+    std::lock_guard<std::mutex> lk(kp->mu);
+    auto it = kp->seqs.find(seq_id);
+    if (it == kp->seqs.end()) return fail(LLATTN_EINVAL, "kvpool_mark_committed: sequence %d is not open", seq_id);
+    const int have = int(it->second.size());
+    if (nblocks > have) return fail(LLATTN_EINVAL, "kvpool_mark_committed: %d blocks, the sequence has %d", nblocks, have);
+    const int n = nblocks < 0 ? have : nblocks;
+    for (int b = 0; b < n; ++b) kp->pages[it->second[b]].committed = true;
     return LLATTN_OK;
 }
 

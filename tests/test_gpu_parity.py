@@ -312,11 +312,13 @@ def test_page_manager_prefix_reuse_end_to_end(api, ctx, orc, pkg):
     sa, ra, pa = mgr.open(ids_a)
     assert ra == 0
     api.kv_commit_paged(dev(Ka), dev(Va), pool, dev(api.KvPool.page_table(pa).T.copy()))
+    mgr.mark_committed(sa)
     torch.cuda.synchronize()
     snap = pool.cpu().numpy().copy()
     sb, rb, pb = mgr.open(ids_b)
     assert rb == 5 and pb[:5].tolist() == pa[:5].tolist()
     api.kv_commit_paged(dev(Kb[rb:]), dev(Vb[rb:]), pool, dev(api.KvPool.page_table(pb[rb:]).T.copy()))
+    mgr.mark_committed(sb)
     torch.cuda.synchronize()
     now = pool.cpu().numpy()
     shared = (pa[:, None] * 4 + np.arange(4)[None, :]).reshape(-1)
@@ -342,6 +344,7 @@ def test_page_manager_prefix_reuse_end_to_end(api, ctx, orc, pkg):
     blk = g.integers(0, 150000, 32, dtype=np.int32)
     page, hit = mgr.append(sa, blk)
     assert not hit and page not in set(pa.tolist()) | set(pb.tolist())
+    mgr.mark_committed(sa)
     mgr.close(sa); mgr.close(sb)
     assert mgr.stats()["cached"] == 8 + 4 + 1
 

@@ -39,6 +39,29 @@ def test_reference_split_policy_helpers(api):
     assert api.chunks_for(0, 8) == 1 and api.chunks_for(1024, 256) == 4 and api.chunks_for(33, 8) == 5
 
 
+def test_shim_default_split_fits_the_reference_engines_partial_buffers():
+    """The source-level shim spreads a context over up to 37 chunks per kv head, while an unmodified engine allocates
+    its partial buffers for 16 query blocks x 4 kv heads x 4 chunks = 256 slots (engine/engine.cu:301-304) and calls
+    pick_bpc with two arguments. The slot index a launch writes stays below nb * 4 * nchunks; this restates the shim's
+    policy (include/attn_shim.cuh) and checks the bound for every batch size and context length the engine can reach."""
+    def shim_pick_bpc(nblocks, nbatch, max_chunks=37):
+        want = max(1, min(max_chunks, (148 + 4 * nbatch - 1) // (4 * nbatch)))
+        bpc = max(1, (nblocks + want - 1) // want)
+        bpc = max(bpc, min(nblocks, 8))
+        return (bpc + 3) // 4 * 4
+    worst = 0
+    for nb in range(1, 17):
+        for nblocks in list(range(0, 300)) + [511, 512, 992, 1007, 1023, 1024, 4095]:
+            vis = nblocks + nb - 1
+            bpc = shim_pick_bpc(vis, nb)
+            nch = 1 if vis <= 0 else (vis + bpc - 1) // bpc
+            worst = max(worst, nb * 4 * nch)
+            assert bpc % 4 == 0 and nb * 4 * nch <= 256, (nb, nblocks, bpc, nch)
+    assert worst <= 192
+    src = open(os.path.join(ROOT, "include", "attn_shim.cuh")).read()
+    assert "static_assert(slots_fit_reference(1)" in src and "MAX_CHUNKS_HINT = 37" in src
+
+
 def test_argument_errors_are_status_codes_without_a_gpu(api):
     L = api.lib()
     assert L.llattn_kv_commit(None, None, None, 4, 0, 1, None) == api.EINVAL

@@ -27,6 +27,7 @@ def test_prefix_reuse_same_prompt(api):
     t = _tokens(1, 32 * 5 + 7)                      # 5 full blocks + a ragged tail that gets no page
     s1, r1, p1 = pool.open(t)
     assert r1 == 0 and len(p1) == 5 and len(set(p1.tolist())) == 5
+    pool.mark_committed(s1)                         # the caller has run the commit kernel on p1
     s2, r2, p2 = pool.open(t)
     assert r2 == 5 and p2.tolist() == p1.tolist()
     st = pool.stats()
@@ -46,6 +47,7 @@ def test_divergence_and_reference_rule(api):
     b = a.copy()
     b[32 * 3 + 5] += 1                               # block 3 differs
     sa, _, pa = pool.open(a)
+    pool.mark_committed(sa)
     sb, rb, pb = pool.open(b)
     keep = 0
     while keep < 6 and np.array_equal(a[keep * 32:(keep + 1) * 32], b[keep * 32:(keep + 1) * 32]):
@@ -61,10 +63,12 @@ def test_append_and_shared_continuation(api):
     pool = api.KvPool(32)
     t = _tokens(3, 64)
     s1, _, _ = pool.open(t)
+    pool.mark_committed(s1)
     s2, r2, _ = pool.open(t)
     assert r2 == 2
     blk = _tokens(4, 32)
     p1, hit1 = pool.append(s1, blk)
+    pool.mark_committed(s1)
     p2, hit2 = pool.append(s2, blk)
     assert not hit1 and hit2 and p1 == p2
     p3, hit3 = pool.append(s2, _tokens(5, 32))
@@ -79,6 +83,7 @@ def test_lru_eviction_and_exhaustion(api):
     a, b, c = _tokens(6, 32 * 4), _tokens(7, 32 * 4), _tokens(8, 32 * 4)
     sa, _, pa = pool.open(a)
     sb, _, pb = pool.open(b)
+    pool.mark_committed(sa); pool.mark_committed(sb)
     with pytest.raises(RuntimeError, match="exhausted"):
         pool.open(c)                                 # every page is held
     st = pool.stats()
@@ -90,10 +95,12 @@ def test_lru_eviction_and_exhaustion(api):
     with pytest.raises(RuntimeError, match="exhausted"):
         pool.open(a)                                 # blocks 0, 1 are cached, but 2, 3 need pages and none is left
     assert pool.stats()["cached"] == 2               # the failed open let go of the two it had found
-    pool.close(sc)
+    pool.close(sc)                                   # never committed: its two pages are free again, not cached
+    assert pool.stats()["free"] == 2 and pool.stats()["cached"] == 2
     s4, r4, p4 = pool.open(a)                        # blocks 0, 1 still cached; 2, 3 were evicted: c's pages recycled
     assert r4 == 2 and p4[:2].tolist() == pa[:2].tolist()
     assert pool.stats()["free"] == 0 and pool.stats()["cached"] == 0
+    pool.mark_committed(s4)
     pool.close(sb); pool.close(s4)
     assert pool.stats()["cached"] == 8
 
@@ -104,9 +111,33 @@ def test_failed_open_rolls_back(api):
     with pytest.raises(RuntimeError, match="exhausted"):
         pool.open(_tokens(10, 32 * 3))
     st = pool.stats()
-    assert st["free"] + st["cached"] == 2            # the two blocks it had taken are available again
-    s2, _, p2 = pool.open(_tokens(11, 64))
-    assert len(p2) == 2
+    assert st["free"] == 2 and st["cached"] == 0     # the two pages it had taken are free again and registered nowhere
+    s2, r2, p2 = pool.open(_tokens(10, 64))          # the same leading blocks as the failed open: nothing to reuse
+    assert r2 == 0 and len(p2) == 2
+    assert pool.stats()["hits"] == 0
+
+
+def test_only_committed_pages_are_reused(api):
+    """A page is reported as reused only after the caller said its records exist; a sequence closed before its commit
+    leaves nothing behind."""
+    pool = api.KvPool(16)
+    t = _tokens(20, 32 * 3)
+    s1, r1, p1 = pool.open(t)
+    s2, r2, p2 = pool.open(t)                        # s1 has not committed yet: same pages, but s2 must prefill too
+    assert r1 == 0 and r2 == 0 and p2.tolist() == p1.tolist()
+    pool.mark_committed(s1, 2)                       # two of the three blocks are written
+    s3, r3, p3 = pool.open(t)
+    assert r3 == 2 and p3.tolist() == p1.tolist()
+    with pytest.raises(RuntimeError, match="blocks"):
+        pool.mark_committed(s1, 4)
+    pool.close(s1); pool.close(s2); pool.close(s3)
+    st = pool.stats()
+    assert st["cached"] == 2 and st["free"] == 14    # the uncommitted third page went back to the free list
+    u = _tokens(21, 64)
+    s4, _, _ = pool.open(u)
+    pool.close(s4)                                   # closed before any commit
+    s5, r5, _ = pool.open(u)
+    assert r5 == 0 and pool.stats()["cached"] == 2
 
 
 def test_errors(api):
