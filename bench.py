@@ -55,6 +55,7 @@ def parse():
     ap.add_argument("--no-graph", action="store_true")
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-e2e", action="store_true")
+    ap.add_argument("--precise", action="store_true", help="time the LLATTN_IO_PRECISE_P path (fp16 P + fp16 remainder) instead of the default")
     ap.add_argument("--dense", action="store_true",
                     help="time the W4.A8 attention-output projection (the consumer of the path) instead; own JSON line")
     return ap.parse_args()
@@ -265,7 +266,7 @@ def run_ours(a):
 
     def step(parts=3):
         for l in range(L):
-            ctx.attention(plans[l], Q[l], Kf[l], Vf[l], O16=O[l], stream=stream, parts=parts)
+            ctx.attention(plans[l], Q[l], Kf[l], Vf[l], O16=O[l], stream=stream, parts=parts, precise=a.precise)
 
     def barrier():
         if world > 1:

@@ -86,7 +86,7 @@ __global__ void __launch_bounds__(ATT_NTH, 1) attn_partial(Args a) {
     p.ref_nchunks = a.nchunks;
     // reference grid (kv head, chunk, query block); gridDim.y may be smaller than nchunks after a graph patch
     if (int(blockIdx.y) >= a.nchunks) return;
-    llattn::attn_tile_body(p, (int(blockIdx.z) * a.nchunks + int(blockIdx.y)) * 4 + int(blockIdx.x));
+    llattn::attn_tile_body<false>(p, (int(blockIdx.z) * a.nchunks + int(blockIdx.y)) * 4 + int(blockIdx.x));
 }
 
 __global__ void __launch_bounds__(32 * COMB_ROWS)

@@ -140,7 +140,16 @@ typedef struct llattn_io {
     float* s8;      /* [nq_total*32][16] */
     int32_t* sum8;  /* [nq_total*32][16] */
     float scale;    /* 0 -> 1/sqrt(128) */
+    uint32_t flags; /* 0, or LLATTN_IO_PRECISE_P */
 } llattn_io;
+
+/* llattn_io.flags. Default (0): the softmax probabilities enter the P.V product as fp16, like the reference kernel's
+ * (engine/attn.cu:261-263); a query row that one key partly dominates then carries that key's fp16 rounding (2^-12
+ * relative), which at long contexts exceeds 2e-3 of the output RMS on a few elements. LLATTN_IO_PRECISE_P carries every
+ * probability as an fp16 value plus an fp16 remainder (two P.V chains per tile): max-abs error against the fp64 oracle
+ * stays within 2e-3 of the output RMS at 32 K tokens, at about two thirds of the throughput. No counterpart in the
+ * reference. */
+#define LLATTN_IO_PRECISE_P 1u
 
 typedef struct llattn_plan_stats {
     int32_t nseq, nq_total, nitems, nslots, nctas;

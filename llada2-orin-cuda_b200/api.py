@@ -21,6 +21,7 @@ KV_BLOCK_BYTES, KOFF_META, VOFF, VOFF_META = 4736, 2048, 2560, 4608
 SCALE = 0.08838834764831845  # 1/sqrt(128), the constant engine/engine.cu:430 passes
 
 OK, EINVAL, ECUDA, ENOMEM, EDEVICE = 0, 1, 2, 3, 4
+IO_PRECISE_P = 1  # llattn_io.flags
 
 EXPORTS = (
     "llattn_version", "llattn_last_error", "llattn_pick_bpc", "llattn_chunks_for", "llattn_tile_units", "llattn_kv_commit",
@@ -51,7 +52,8 @@ class _Seq(Structure):
 
 class _IO(Structure):
     _fields_ = [("Q", c_void_p), ("Kf", c_void_p), ("Vf", c_void_p), ("O16", c_void_p), ("O32", c_void_p),
-                ("LSE", c_void_p), ("q8", c_void_p), ("s8", c_void_p), ("sum8", c_void_p), ("scale", c_float)]
+                ("LSE", c_void_p), ("q8", c_void_p), ("s8", c_void_p), ("sum8", c_void_p), ("scale", c_float),
+                ("flags", ctypes.c_uint32)]
 
 
 class PlanStats(Structure):
@@ -296,15 +298,18 @@ class Context:
         return Plan(self, seqs, nctas)
 
     def attention(self, plan: "Plan", Q, Kf, Vf, O16=None, O32=None, LSE=None, q8=None, s8=None, sum8=None,
-                  scale: float = 0.0, stream=None, parts: int = 3) -> None:
-        """parts: 3 = tile kernel + merge (the normal pass); 1 / 2 run one of the two kernels (per-kernel timing)."""
-        io = _IO(_ptr(Q), _ptr(Kf), _ptr(Vf), _ptr(O16), _ptr(O32), _ptr(LSE), _ptr(q8), _ptr(s8), _ptr(sum8), scale)
+                  scale: float = 0.0, stream=None, parts: int = 3, precise: bool = False) -> None:
+        """parts: 3 = tile kernel + merge (the normal pass); 1 / 2 run one of the two kernels (per-kernel timing).
+        precise: carry the softmax probabilities as fp16 value + fp16 remainder (LLATTN_IO_PRECISE_P)."""
+        io = _IO(_ptr(Q), _ptr(Kf), _ptr(Vf), _ptr(O16), _ptr(O32), _ptr(LSE), _ptr(q8), _ptr(s8), _ptr(sum8), scale,
+                 IO_PRECISE_P if precise else 0)
         _check(lib().llattn_attention_parts(self._h, plan._h, byref(io), parts, _stream(stream)))
 
     def attention_host(self, plan: "Plan", Q, Kf, Vf, O16=None, O32=None, LSE=None, q8=None, s8=None, sum8=None,
-                       scale: float = 0.0, stream=None) -> None:
+                       scale: float = 0.0, stream=None, precise: bool = False) -> None:
         """Q/Kf/Vf and the outputs are HOST tensors (pinned for asynchronous copies)."""
-        io = _IO(_ptr(Q), _ptr(Kf), _ptr(Vf), _ptr(O16), _ptr(O32), _ptr(LSE), _ptr(q8), _ptr(s8), _ptr(sum8), scale)
+        io = _IO(_ptr(Q), _ptr(Kf), _ptr(Vf), _ptr(O16), _ptr(O32), _ptr(LSE), _ptr(q8), _ptr(s8), _ptr(sum8), scale,
+                 IO_PRECISE_P if precise else 0)
         _check(lib().llattn_attention_host(self._h, plan._h, byref(io), _stream(stream)))
 
     def host_flush(self, stream=None) -> None:

@@ -246,16 +246,23 @@ __device__ __forceinline__ float rowmax16(const uint32_t (&r)[16]) {
     }
     return max3(max3(a, b, __uint_as_float(r[7])), __uint_as_float(r[15]), __uint_as_float(r[15]));
 }
-// Score pairs J0 .. J1-1 of 16 scores -> packed fp16 p.
-template <int J0, int J1>
-__device__ __forceinline__ void exp_pairs16(const uint32_t (&r)[16], uint32_t* pk, unsigned long long sl2x2, unsigned long long nm2) {
+// Score pairs J0 .. J1-1 of 16 scores -> packed fp16 p. PRECISE: also the fp16 remainder p - fp16(p) (exact in fp32, then
+// rounded once more: together the pair carries p to about 22 bits).
+template <int J0, int J1, bool PRECISE>
+__device__ __forceinline__ void exp_pairs16(const uint32_t (&r)[16], uint32_t* pk, uint32_t* pkl, unsigned long long sl2x2, unsigned long long nm2) {
 #pragma unroll
     for (int j = J0; j < J1; ++j) {
         if (LLATTN_SKIP & 2) { pk[j] = r[2 * j] & 0x03ff03ffu; continue; }
         float x0, x1;
         fma2(r[2 * j], r[2 * j + 1], sl2x2, nm2, x0, x1);
-        const half2 h = __floats2half2_rn(ex2(x0), ex2(x1));
+        const float e0 = ex2(x0), e1 = ex2(x1);
+        const half2 h = __floats2half2_rn(e0, e1);
         pk[j] = *reinterpret_cast<const uint32_t*>(&h);
+        if (PRECISE) {
+            const float2 hf = __half22float2(h);
+            const half2 l = __floats2half2_rn(e0 - hf.x, e1 - hf.y);
+            pkl[j] = *reinterpret_cast<const uint32_t*>(&l);
+        }
     }
 }
 
@@ -266,7 +273,7 @@ __device__ __forceinline__ void exp_pairs16(const uint32_t (&r)[16], uint32_t* p
 // of line so that the common path stays small.
 // tlane: tensor-memory address of the warp's lanes at column 0; ts: the tile's S / P buffer; bar_pv, par_pv: barrier and
 // parity of "PV of the previous tile has completed". Returns the row's new reference, NaN when that wait ran out.
-__device__ __noinline__ float raise_reference(float mref, float cs, bool over, int chunks_done, bool have_acc, uint32_t tlane,
+__device__ __noinline__ float raise_reference(float mref, float cs, bool over, int chunks_done, bool have_acc, bool precise, uint32_t tlane,
                                               uint32_t ts, uint32_t bar_pv, uint32_t par_pv, volatile int* abort_flag) {
     const float mnew = over ? cs : mref;
     const float corr = over ? ex2(mref - mnew) : 1.f;      // 0 for a row that had no reference yet
@@ -289,17 +296,19 @@ __device__ __noinline__ float raise_reference(float mref, float cs, bool over, i
         ptx::tmem_st16(tlane + TM_L, r);
     }
     const half2 ch = __float2half2_rn(corr);
+    // P chunk pc sits in columns 32 pc .. 32 pc + 15, its remainder (precise mode) in the 16 columns after them
 #pragma unroll 1
-    for (int pc = 0; pc < chunks_done; ++pc) {
+    for (int pc = 0; pc < (precise ? 2 : 1) * chunks_done; ++pc) {
         uint32_t r[16];
-        ptx::tmem_ld16(ts + 32 * pc, r);
+        const uint32_t col = precise ? 16 * pc : 32 * pc;
+        ptx::tmem_ld16(ts + col, r);
         ptx::tmem_wait_ld_tied(r);
 #pragma unroll
         for (int j = 0; j < 16; ++j) {
             const half2 h = __hmul2(*reinterpret_cast<const half2*>(&r[j]), ch);
             r[j] = *reinterpret_cast<const uint32_t*>(&h);
         }
-        ptx::tmem_st16(ts + 32 * pc, r);
+        ptx::tmem_st16(ts + col, r);
     }
     ptx::tmem_wait_st();
     return mnew;
@@ -311,7 +320,7 @@ __device__ __noinline__ float raise_reference(float mref, float cs, bool over, i
 // goes back over the first 16 of the 32 S columns it came from. Before the last chunk's exponentials the barrier of the
 // next tile's S is tested (next_bar != 0), so that the test's latency is covered and the next tile starts without a wait
 // when its S is already there. Returns false when a wait of the rare path ran out.
-template <int NU>
+template <int NU, bool PRECISE>
 __device__ __forceinline__ bool softmax_tile(float& mref, float sl2, unsigned long long sl2x2, uint32_t tlane, uint32_t ts, bool have_acc,
                                              uint32_t bar_pv, uint32_t par_pv, volatile int* abort_flag, uint32_t next_bar, uint32_t next_par,
                                              bool& next_ready) {
@@ -330,20 +339,22 @@ __device__ __forceinline__ bool softmax_tile(float& mref, float sl2, unsigned lo
         const float cs = cm * sl2;
         const bool over = cs > mref + RESCALE_SLACK;
         if (__any_sync(0xffffffffu, over)) {
-            mref = raise_reference(mref, cs, over, c, have_acc, tlane, ts, bar_pv, par_pv, abort_flag);
+            mref = raise_reference(mref, cs, over, c, have_acc, PRECISE, tlane, ts, bar_pv, par_pv, abort_flag);
             if (__any_sync(0xffffffffu, mref != mref)) return false;
             nm2 = dup2(-mref);
         }
-        uint32_t pk[16];
+        uint32_t pk[16], pkl[PRECISE ? 16 : 1];
         if (c + 1 < NU) ptx::tmem_ld16(ts + 32 * (c + 1), n0);
         else next_ready = next_bar != 0 && ptx::mbar_try_wait(next_bar, next_par);
-        exp_pairs16<0, 8>(c0, pk, sl2x2, nm2);
+        exp_pairs16<0, 8, PRECISE>(c0, pk, pkl, sl2x2, nm2);
         ptx::tmem_st8(ts + 32 * c, pk);
         if (c + 1 < NU) ptx::tmem_ld16(ts + 32 * (c + 1) + 16, n1);
-        exp_pairs16<0, 5>(c1, pk + 8, sl2x2, nm2);
+        exp_pairs16<0, 5, PRECISE>(c1, pk + 8, pkl + (PRECISE ? 8 : 0), sl2x2, nm2);
         if (c + 1 < NU) { ptx::tmem_wait_ld_tied(n0, n1); cm = fmaxf(rowmax16(n0), rowmax16(n1)); }
-        exp_pairs16<5, 8>(c1, pk + 8, sl2x2, nm2);
+        exp_pairs16<5, 8, PRECISE>(c1, pk + 8, pkl + (PRECISE ? 8 : 0), sl2x2, nm2);
         ptx::tmem_st8(ts + 32 * c + 8, pk + 8);
+        // the remainders go over the second half of the chunk's S columns: all 32 have been read by now
+        if (PRECISE) { ptx::tmem_st8(ts + 32 * c + 16, pkl); ptx::tmem_st8(ts + 32 * c + 24, pkl + 8); }
     }
     return true;
 }
@@ -434,6 +445,9 @@ __device__ __forceinline__ void copy_fresh(const half* src, uint8_t* tile_unit, 
 
 // The whole CTA's work. `cta` is the CTA's index in the plan (list mode) or in the flattened reference grid
 // (kv head fastest, then chunk, then query block).
+// PRECISE: P is carried as fp16 value + fp16 remainder (two PV chains per tile), for callers that need the result to
+// within 2e-3 of the output RMS at long contexts and accept about half the throughput.
+template <bool PRECISE>
 __device__ __forceinline__ void attn_tile_body(const KParams& p, const int cta) {
     extern __shared__ __align__(1024) uint8_t smem[];
     uint64_t* bars = reinterpret_cast<uint64_t*>(smem + SM_BAR);
@@ -537,10 +551,10 @@ __device__ __forceinline__ void attn_tile_body(const KParams& p, const int cta) 
                     mref = mx * p.sl2;
                 }
                 bool ok;
-                if (nu == TILE_UNITS) ok = softmax_tile<TILE_UNITS>(mref, p.sl2, sl2x2, tlane, ts, i > 0, bar_pv, par_pv, abort_flag, next_bar, next_par, s_ready);      // every tile of a run but its last
-                else if (nu == 3) ok = softmax_tile<3>(mref, p.sl2, sl2x2, tlane, ts, i > 0, bar_pv, par_pv, abort_flag, next_bar, next_par, s_ready);
-                else if (nu == 2) ok = softmax_tile<2>(mref, p.sl2, sl2x2, tlane, ts, i > 0, bar_pv, par_pv, abort_flag, next_bar, next_par, s_ready);
-                else ok = softmax_tile<1>(mref, p.sl2, sl2x2, tlane, ts, i > 0, bar_pv, par_pv, abort_flag, next_bar, next_par, s_ready);
+                if (nu == TILE_UNITS) ok = softmax_tile<TILE_UNITS, PRECISE>(mref, p.sl2, sl2x2, tlane, ts, i > 0, bar_pv, par_pv, abort_flag, next_bar, next_par, s_ready);      // every tile of a run but its last
+                else if (nu == 3) ok = softmax_tile<3, PRECISE>(mref, p.sl2, sl2x2, tlane, ts, i > 0, bar_pv, par_pv, abort_flag, next_bar, next_par, s_ready);
+                else if (nu == 2) ok = softmax_tile<2, PRECISE>(mref, p.sl2, sl2x2, tlane, ts, i > 0, bar_pv, par_pv, abort_flag, next_bar, next_par, s_ready);
+                else ok = softmax_tile<1, PRECISE>(mref, p.sl2, sl2x2, tlane, ts, i > 0, bar_pv, par_pv, abort_flag, next_bar, next_par, s_ready);
                 if (!ok) { alive = false; errbits |= ERR_WAIT_SOFTMAX; }
                 if (!alive) break;
                 ptx::tmem_wait_st();
@@ -769,13 +783,19 @@ __device__ __forceinline__ void attn_tile_body(const KParams& p, const int cta) 
                 {
                     const uint32_t pb = tmem + TM_S + b * 128, vlo = b ? vlo1 : vlo0;
                     if (nu == TILE_UNITS) {
-                        ptx::mma_ts_pv8_warp(tmem + TM_O, pb, vlo, vhi, idO, i == 0 ? 0u : 1u, BAR(B_PV_DONE + b));
+                        if (PRECISE) {
+                            ptx::mma_ts_pv8_warp<false>(tmem + TM_O, pb, vlo, vhi, idO, i == 0 ? 0u : 1u, 0u);
+                            ptx::mma_ts_pv8_warp<true>(tmem + TM_O, pb + 16, vlo, vhi, idO, 1u, BAR(B_PV_DONE + b));     // the remainders of P
+                        } else {
+                            ptx::mma_ts_pv8_warp<true>(tmem + TM_O, pb, vlo, vhi, idO, i == 0 ? 0u : 1u, BAR(B_PV_DONE + b));
+                        }
                     } else {
 #pragma unroll
                         for (int u = 0; u < TILE_UNITS - 1; ++u)
                             if (u < nu) {
                                 const uint64_t d0 = (uint64_t(vhi) << 32) | (vlo + 256u * u);
                                 ptx::mma_ts_x2_warp(tmem + TM_O, pb + 32 * u, d0, d0 + 128, idO, (i == 0 && u == 0) ? 0u : 1u);
+                                if (PRECISE) ptx::mma_ts_x2_warp(tmem + TM_O, pb + 32 * u + 16, d0, d0 + 128, idO, 1u);
                             }
                         ptx::mma_commit_warp(BAR(B_PV_DONE + b));
                     }
@@ -851,13 +871,19 @@ __device__ __forceinline__ void attn_tile_body(const KParams& p, const int cta) 
                     // unit u = keys 32u..32u+31 = K-steps 2u, 2u+1; its P sits at columns 32u .. 32u+15 of the S buffer
                     const uint32_t pb = tmem + TM_S + b * 128, vlo = b ? vlo1 : vlo0;
                     if (nu == TILE_UNITS) {
-                        ptx::mma_ts_pv8_warp(tmem + TM_O, pb, vlo, vhi, idO, i == 0 ? 0u : 1u, BAR(B_PV_DONE + b));
+                        if (PRECISE) {
+                            ptx::mma_ts_pv8_warp<false>(tmem + TM_O, pb, vlo, vhi, idO, i == 0 ? 0u : 1u, 0u);
+                            ptx::mma_ts_pv8_warp<true>(tmem + TM_O, pb + 16, vlo, vhi, idO, 1u, BAR(B_PV_DONE + b));     // the remainders of P
+                        } else {
+                            ptx::mma_ts_pv8_warp<true>(tmem + TM_O, pb, vlo, vhi, idO, i == 0 ? 0u : 1u, BAR(B_PV_DONE + b));
+                        }
                     } else {
 #pragma unroll
                         for (int u = 0; u < TILE_UNITS - 1; ++u)
                             if (u < nu) {
                                 const uint64_t d0 = (uint64_t(vhi) << 32) | (vlo + 256u * u);
                                 ptx::mma_ts_x2_warp(tmem + TM_O, pb + 32 * u, d0, d0 + 128, idO, (i == 0 && u == 0) ? 0u : 1u);
+                                if (PRECISE) ptx::mma_ts_x2_warp(tmem + TM_O, pb + 32 * u + 16, d0, d0 + 128, idO, 1u);
                             }
                         ptx::mma_commit_warp(BAR(B_PV_DONE + b));
                     }
@@ -880,8 +906,9 @@ __device__ __forceinline__ void attn_tile_body(const KParams& p, const int cta) 
     if (warp == WARP_MMA) ptx::tmem_dealloc(tmem, TMEM_COLS);
 }
 
+template <bool PRECISE>
 __global__ void __launch_bounds__(ATTN_THREADS, 1) attn_tile_kernel(const __grid_constant__ KParams p) {
-    attn_tile_body(p, blockIdx.x);
+    attn_tile_body<PRECISE>(p, blockIdx.x);
 }
 
 }  // namespace llattn

@@ -88,7 +88,8 @@ int ensure_kernel_attrs() {
     CU(cudaGetDevice(&dev));
     std::lock_guard<std::mutex> lk(mu);
     if (dev < 64 && done[dev]) return LLATTN_OK;
-    CU(cudaFuncSetAttribute(llattn::attn_tile_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, llattn::ATTN_SMEM_BYTES));
+    CU(cudaFuncSetAttribute(llattn::attn_tile_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, llattn::ATTN_SMEM_BYTES));
+    CU(cudaFuncSetAttribute(llattn::attn_tile_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, llattn::ATTN_SMEM_BYTES));
     if (dev < 64) done[dev] = true;
     return LLATTN_OK;
 }
@@ -264,7 +265,7 @@ extern "C" int llattn_attention_static(const void* Q, const void* Kf, const void
     p.ref_seq = SeqDesc{static_cast<const uint8_t*>(cache), nullptr, max_blocks, nblocks, nb, 0};
     p.ref_bpc = bpc;
     p.ref_nchunks = nchunks;
-    attn_tile_kernel<<<NKV * nchunks * nb, ATTN_THREADS, ATTN_SMEM_BYTES, as_stream(stream)>>>(p);
+    attn_tile_kernel<false><<<NKV * nchunks * nb, ATTN_THREADS, ATTN_SMEM_BYTES, as_stream(stream)>>>(p);
     CU(cudaGetLastError());
     MergeOut o{static_cast<half*>(O16), O32, LSE, q8, s8, sum8};
     combine_ref_kernel<<<dim3(NKV, QR / MERGE_ROWS, nb), MERGE_THREADS, 0, as_stream(stream)>>>(Opart, Mpart, Lpart, nchunks, nblocks, bpc, o);

@@ -91,6 +91,7 @@ int check_io(const llattn_io* io, const char* who) {
     if (!io || !io->Q || !io->Kf || !io->Vf) return fail(LLATTN_EINVAL, "%s: Q, Kf and Vf are required", who);
     if (!io->O16 && !io->O32 && !io->q8 && !io->LSE) return fail(LLATTN_EINVAL, "%s: no output requested", who);
     if (io->q8 && (!io->s8 || !io->sum8)) return fail(LLATTN_EINVAL, "%s: q8 needs s8 and sum8", who);
+    if (io->flags & ~uint32_t(LLATTN_IO_PRECISE_P)) return fail(LLATTN_EINVAL, "%s: unknown flag bits 0x%x", who, io->flags);
     return LLATTN_OK;
 }
 
@@ -120,7 +121,7 @@ int llattn_attn_partial(const llattn_args* a, int nb, int* err_word, void* strea
     p.ref_seq = SeqDesc{static_cast<const uint8_t*>(a->cache), nullptr, a->max_blocks, a->nblocks, nb, 0};
     p.ref_bpc = a->blocks_per_chunk;
     p.ref_nchunks = a->nchunks;
-    attn_tile_kernel<<<NKV * a->nchunks * nb, ATTN_THREADS, ATTN_SMEM_BYTES, as_stream(stream)>>>(p);
+    attn_tile_kernel<false><<<NKV * a->nchunks * nb, ATTN_THREADS, ATTN_SMEM_BYTES, as_stream(stream)>>>(p);
     CU(cudaGetLastError());
     return LLATTN_OK;
 }
@@ -292,7 +293,8 @@ int llattn_attention_parts(llattn_ctx* c, const llattn_plan* pl, const llattn_io
     p.sl2 = (io->scale > 0.f ? io->scale : 0.08838834764831845f) * 1.4426950408889634f;
     p.err = c->err_word;
     if (parts & 1) {
-        attn_tile_kernel<<<pl->stats.nctas, ATTN_THREADS, ATTN_SMEM_BYTES, as_stream(stream)>>>(p);
+        if (io->flags & LLATTN_IO_PRECISE_P) attn_tile_kernel<true><<<pl->stats.nctas, ATTN_THREADS, ATTN_SMEM_BYTES, as_stream(stream)>>>(p);
+        else attn_tile_kernel<false><<<pl->stats.nctas, ATTN_THREADS, ATTN_SMEM_BYTES, as_stream(stream)>>>(p);
         CU(cudaGetLastError());
     }
     if (parts & 2) {
@@ -343,7 +345,7 @@ int llattn_attention_host(llattn_ctx* c, const llattn_plan* pl, const llattn_io*
     uint8_t* dQ = d; d += up(bQ);
     uint8_t* dK = d; d += up(bKV);
     uint8_t* dV = d; d += up(bKV);
-    dio.Q = dQ; dio.Kf = dK; dio.Vf = dV; dio.scale = h->scale;
+    dio.Q = dQ; dio.Kf = dK; dio.Vf = dV; dio.scale = h->scale; dio.flags = h->flags;
     if (bO16) { dio.O16 = d; d += up(bO16); }
     if (bO32) { dio.O32 = reinterpret_cast<float*>(d); d += up(bO32); }
     if (bLSE) { dio.LSE = reinterpret_cast<float*>(d); d += up(bLSE); }

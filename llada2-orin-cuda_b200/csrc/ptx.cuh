@@ -251,7 +251,8 @@ __device__ __forceinline__ void mma_ts_s8_warp(uint32_t d_tmem, uint32_t a_tmem,
         : "memory");
 }
 // O (+)= P V over a full tile of four 32-key units from one base descriptor: K-step j (16 keys) adds 128 16-byte units;
-// the P of unit u sits at columns 32u .. 32u+15 of the S buffer, 8 columns per K-step. One commit.
+// the P of unit u sits at columns 32u .. 32u+15 of the S buffer, 8 columns per K-step. One commit (COMMIT), or none.
+template <bool COMMIT>
 __device__ __forceinline__ void mma_ts_pv8_warp(uint32_t d_tmem, uint32_t p_tmem, uint32_t b_lo, uint32_t b_hi, uint32_t idesc,
                                                 uint32_t accumulate_first, uint32_t bar) {
     asm volatile(
@@ -274,9 +275,10 @@ __device__ __forceinline__ void mma_ts_pv8_warp(uint32_t d_tmem, uint32_t p_tmem
         "@pe tcgen05.mma.cta_group::1.kind::f16 [%0], [a], db, %4, pt;\n\t"
         "add.u32 a, %1, 104;\n\t add.u32 l, %2, 896;\n\t mov.b64 db, {l, %3};\n\t"
         "@pe tcgen05.mma.cta_group::1.kind::f16 [%0], [a], db, %4, pt;\n\t"
-        "@pe tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%6];\n\t"
+        "setp.ne.b32 pt, %7, 0;\n\t and.pred pt, pt, pe;\n\t"
+        "@pt tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%6];\n\t"
         "}\n"
-        :: "r"(d_tmem), "r"(p_tmem), "r"(b_lo), "r"(b_hi), "r"(idesc), "r"(accumulate_first), "r"(bar)
+        :: "r"(d_tmem), "r"(p_tmem), "r"(b_lo), "r"(b_hi), "r"(idesc), "r"(accumulate_first), "r"(bar), "n"(COMMIT ? 1 : 0)
         : "memory");
 }
 // Two K-steps (one 32-key unit) of D (+)= A[tmem] * B[smem]; A advances 8 TMEM columns.
