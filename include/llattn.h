@@ -141,6 +141,11 @@ typedef struct llattn_io {
     int32_t* sum8;  /* [nq_total*32][16] */
     float scale;    /* 0 -> 1/sqrt(128) */
     uint32_t flags; /* 0, or LLATTN_IO_PRECISE_P */
+    int64_t cache_offset; /* bytes added to every sequence's `cache` pointer in this call (multiple of 16). The layers of a
+                             model keep their caches (or record pools) a fixed distance apart (engine/engine.cu:233 allocates
+                             one cache per layer, all of one size): one plan then serves all layers of a step, layer l
+                             being called with cache_offset = l * (bytes between two layers' caches). 0 for a plan whose
+                             `cache` pointers already name the layer. */
 } llattn_io;
 
 /* llattn_io.flags. Default (0): the softmax probabilities enter the P.V product as fp16, like the reference kernel's
@@ -152,7 +157,7 @@ typedef struct llattn_io {
 #define LLATTN_IO_PRECISE_P 1u
 
 typedef struct llattn_plan_stats {
-    int32_t nseq, nq_total, nitems, nslots, nctas;
+    int32_t nseq, nq_total, nitems, nslots, nctas;   /* nctas: CTAs that got work (the launch may have more) */
     int64_t total_units;       /* records + fresh blocks over all (query block, kv head) pairs */
     int64_t max_cta_units;     /* units of the busiest CTA */
     size_t workspace_bytes;    /* partial-result scratch the plan needs (owned by the context) */
@@ -162,23 +167,33 @@ int llattn_create(int device, llattn_ctx** out);
 void llattn_destroy(llattn_ctx* ctx);
 
 /* Builds the work list for `nseq` sequences (host array) and uploads it; allocates, so not for use inside stream
- * capture. `nctas` <= 0 means one CTA per SM. The plan stays valid until the lengths or pointers change. */
+ * capture. `nctas` <= 0 means one CTA per SM. Every launch of the plan has exactly that many CTAs. */
 int llattn_plan_create(llattn_ctx* ctx, const llattn_seq* seqs_host, int nseq, int nctas, llattn_plan** out);
 void llattn_plan_destroy(llattn_plan* plan);
 int llattn_plan_get_stats(const llattn_plan* plan, llattn_plan_stats* out);
 
+/* New lengths (and cache / page-table pointers) for an existing plan, without allocation or device synchronisation:
+ * the work list is rebuilt on the host into the plan's pinned mirror and copied over the plan's device blob with one
+ * cudaMemcpyAsync on `stream`; launches ordered after it on that stream see the new plan. The sequences keep their
+ * number and their query-block counts (nq, q_first); contexts may grow or shrink freely. A CUDA graph that captured
+ * llattn_attention with this plan stays valid: the kernel reads lengths, work items and tile descriptors from the
+ * plan's device memory and its grid does not change, so a committed block needs this one call and no node patching
+ * (the reference rewrites the parameters of 40 graph nodes instead, engine/engine.cu:533-562). The only wait is for the
+ * previous update's copy to have left the pinned mirror. Not for use inside stream capture (it issues a copy). */
+int llattn_plan_update(llattn_plan* plan, const llattn_seq* seqs_host, int nseq, void* stream);
+
 /* The planner alone, on the host (no CUDA call): statistics of the plan llattn_plan_create would build and, when the
  * arrays are given, its work items (8 int32 each: sequence, query block, kv head, first record, record count, fresh
- * flag, partial slot, 0) and the per-CTA item ranges (nctas + 1 bounds). For sizing and for host-side tests. */
+ * flag, partial slot, output tile) and the per-CTA item ranges (nctas + 1 bounds, nctas = the CTAs that got work). For
+ * sizing and for host-side tests. */
 int llattn_plan_preview(const llattn_seq* seqs_host, int nseq, int nctas, llattn_plan_stats* stats, int32_t* items_out,
                         int max_items, int32_t* cta_first_out, int max_ctas);
 
-/* One attention pass over every sequence of the plan: kernel launches only (two), no allocation, no host sync. */
+/* One attention pass over every sequence of the plan: ONE kernel launch, no allocation, no host sync. A (query block,
+ * kv head) tile that one CTA handles alone is normalised and written by that CTA; a tile spread over several CTAs is
+ * folded together by whichever of them finishes last (it reads the others' partial results from the context's scratch,
+ * in a fixed order, so results do not depend on timing). Calls that share a context must not overlap on the GPU. */
 int llattn_attention(llattn_ctx* ctx, const llattn_plan* plan, const llattn_io* io, void* stream);
-
-/* The same pass one kernel at a time, for per-kernel timing: parts = 1 runs only the tile kernel (partials into the
- * context's scratch), 2 only the merge of the partials already there, 3 both (= llattn_attention). */
-int llattn_attention_parts(llattn_ctx* ctx, const llattn_plan* plan, const llattn_io* io, int parts, void* stream);
 
 /* Same, with Q/Kf/Vf and the requested outputs in HOST memory (pinned, so the copies are asynchronous). The KV cache
  * stays on the device, as in the reference engine. Consecutive calls are pipelined: a call's inputs go up on the

@@ -27,7 +27,7 @@ EXPORTS = (
     "llattn_version", "llattn_last_error", "llattn_pick_bpc", "llattn_chunks_for", "llattn_tile_units", "llattn_kv_commit",
     "llattn_kv_commit_paged", "llattn_qk_norm_rope", "llattn_attn_partial", "llattn_attn_combine", "llattn_create", "llattn_destroy",
     "llattn_plan_create", "llattn_plan_destroy", "llattn_plan_get_stats", "llattn_plan_preview", "llattn_attention",
-    "llattn_attention_parts", "llattn_attention_host", "llattn_host_flush", "llattn_device_status",
+    "llattn_plan_update", "llattn_attention_host", "llattn_host_flush", "llattn_device_status",
     "llattn_dense_w4a8", "llattn_kvpool_create", "llattn_kvpool_destroy", "llattn_kvpool_open", "llattn_kvpool_append", "llattn_kvpool_pages", "llattn_kvpool_mark_committed",
     "llattn_kvpool_close", "llattn_kvpool_stats", "llattn_attention_static",
 )
@@ -53,7 +53,7 @@ class _Seq(Structure):
 class _IO(Structure):
     _fields_ = [("Q", c_void_p), ("Kf", c_void_p), ("Vf", c_void_p), ("O16", c_void_p), ("O32", c_void_p),
                 ("LSE", c_void_p), ("q8", c_void_p), ("s8", c_void_p), ("sum8", c_void_p), ("scale", c_float),
-                ("flags", ctypes.c_uint32)]
+                ("flags", ctypes.c_uint32), ("cache_offset", c_int64)]
 
 
 class PlanStats(Structure):
@@ -91,7 +91,7 @@ def lib() -> ctypes.CDLL:
         L.llattn_plan_get_stats.argtypes = [c_void_p, POINTER(PlanStats)]
         L.llattn_plan_preview.argtypes = [POINTER(_Seq), c_int, c_int, POINTER(PlanStats), c_void_p, c_int, c_void_p, c_int]
         L.llattn_attention.argtypes = [c_void_p, c_void_p, POINTER(_IO), c_void_p]
-        L.llattn_attention_parts.argtypes = [c_void_p, c_void_p, POINTER(_IO), c_int, c_void_p]
+        L.llattn_plan_update.argtypes = [c_void_p, POINTER(_Seq), c_int, c_void_p]
         L.llattn_attention_host.argtypes = [c_void_p, c_void_p, POINTER(_IO), c_void_p]
         L.llattn_host_flush.argtypes = [c_void_p, c_void_p]
         L.llattn_dense_w4a8.argtypes = [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_void_p, c_void_p]
@@ -298,18 +298,18 @@ class Context:
         return Plan(self, seqs, nctas)
 
     def attention(self, plan: "Plan", Q, Kf, Vf, O16=None, O32=None, LSE=None, q8=None, s8=None, sum8=None,
-                  scale: float = 0.0, stream=None, parts: int = 3, precise: bool = False) -> None:
-        """parts: 3 = tile kernel + merge (the normal pass); 1 / 2 run one of the two kernels (per-kernel timing).
-        precise: carry the softmax probabilities as fp16 value + fp16 remainder (LLATTN_IO_PRECISE_P)."""
+                  scale: float = 0.0, stream=None, precise: bool = False, cache_offset: int = 0) -> None:
+        """One launch. precise: carry the softmax probabilities as fp16 value + fp16 remainder (LLATTN_IO_PRECISE_P).
+        cache_offset: bytes added to every sequence's cache pointer (the layer, when one plan serves all layers)."""
         io = _IO(_ptr(Q), _ptr(Kf), _ptr(Vf), _ptr(O16), _ptr(O32), _ptr(LSE), _ptr(q8), _ptr(s8), _ptr(sum8), scale,
-                 IO_PRECISE_P if precise else 0)
-        _check(lib().llattn_attention_parts(self._h, plan._h, byref(io), parts, _stream(stream)))
+                 IO_PRECISE_P if precise else 0, cache_offset)
+        _check(lib().llattn_attention(self._h, plan._h, byref(io), _stream(stream)))
 
     def attention_host(self, plan: "Plan", Q, Kf, Vf, O16=None, O32=None, LSE=None, q8=None, s8=None, sum8=None,
-                       scale: float = 0.0, stream=None, precise: bool = False) -> None:
+                       scale: float = 0.0, stream=None, precise: bool = False, cache_offset: int = 0) -> None:
         """Q/Kf/Vf and the outputs are HOST tensors (pinned for asynchronous copies)."""
         io = _IO(_ptr(Q), _ptr(Kf), _ptr(Vf), _ptr(O16), _ptr(O32), _ptr(LSE), _ptr(q8), _ptr(s8), _ptr(sum8), scale,
-                 IO_PRECISE_P if precise else 0)
+                 IO_PRECISE_P if precise else 0, cache_offset)
         _check(lib().llattn_attention_host(self._h, plan._h, byref(io), _stream(stream)))
 
     def host_flush(self, stream=None) -> None:
@@ -329,6 +329,16 @@ class Plan:
         arr = (_Seq * len(seqs))(*[s._c() for s in seqs])
         self._h = c_void_p()
         _check(lib().llattn_plan_create(ctx._h, arr, len(seqs), nctas, byref(self._h)))
+        st = PlanStats()
+        _check(lib().llattn_plan_get_stats(self._h, byref(st)))
+        self.stats = st
+
+    def update(self, seqs: Sequence[Seq], stream=None) -> None:
+        """New lengths / pointers for the same sequences (llattn_plan_update): no allocation, one asynchronous copy
+        on `stream`; a captured graph that uses this plan stays valid."""
+        arr = (_Seq * len(seqs))(*[s._c() for s in seqs])
+        _check(lib().llattn_plan_update(self._h, arr, len(seqs), _stream(stream)))
+        self._keep = list(seqs)
         st = PlanStats()
         _check(lib().llattn_plan_get_stats(self._h, byref(st)))
         self.stats = st

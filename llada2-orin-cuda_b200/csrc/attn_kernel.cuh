@@ -19,8 +19,10 @@
 //                   computed from). The reference exponent mref is the exact row maximum of the run's first tile and
 //                   moves only when a later score exceeds it by more than 8 in log2 units (engine/attn.cu:237-255
 //                   rescales lazily in the same way); that rare path rescales O in tensor memory, out of line
-// The run's un-normalised O (fp32), reference maximum (log2 units) and row sum go to a partial slot in the format of
-// the reference's Opart/Mpart/Lpart (engine/attn.cu:291-305); merge_kernel.cuh folds the slots of a tile together.
+// A run that is a tile's only one normalises and writes the outputs in its epilogue. Otherwise its un-normalised O (fp32),
+// reference maximum (log2 units) and row sum go to a partial slot in the format of the reference's Opart/Mpart/Lpart
+// (engine/attn.cu:291-305), and the run that arrives last at the tile folds the slots together (merge_kernel.cuh has the
+// row routines); with the reference-shaped operator pair the caller's attn_combine launch does that instead.
 //
 // Operands. Q (the A operand of S = Q K^T) lives in tensor memory for the whole item: row i in lane i, 64 columns of
 // fp16 pairs. K and V tiles live in shared memory in the 128-byte-swizzle layout: a tile is made of blocks of
@@ -37,6 +39,7 @@
 #include <cuda_fp16.h>
 #include "common.cuh"
 #include "ptx.cuh"
+#include "merge_kernel.cuh"
 
 namespace llattn {
 
@@ -128,6 +131,11 @@ struct KParams {
     float* Lpart;
     float sl2;                     // softmax scale * log2(e)
     int* err;
+    // list mode with fused merge (merge != nullptr): the run that completes an output tile writes the tile's outputs
+    const MergeDesc* merge;        // per output tile (WorkItem::tile indexes it)
+    int* tile_counters;            // [tiles][4]: runs of the tile whose rows of lane quarter w are out; back at 0 after the launch
+    MergeOut out;
+    size_t cache_offset;           // bytes added to every sequence's cache pointer: the layer this launch reads
     // reference-grid mode (items == nullptr): CTA i is (kvh = i % 4, chunk = (i / 4) % ref_nchunks, jb = i / (4 * ref_nchunks))
     SeqDesc ref_seq;
     int ref_bpc;
@@ -138,6 +146,7 @@ __device__ __forceinline__ bool fetch_item(const KParams& p, int idx, WorkItem& 
     if (p.items) {
         w = p.items[idx];
         s = p.seqs[w.seq];
+        s.cache += p.cache_offset;
         return true;
     }
     const int kvh = idx & 3, chunk = (idx >> 2) % p.ref_nchunks, jb = (idx >> 2) / p.ref_nchunks;
@@ -150,7 +159,7 @@ __device__ __forceinline__ bool fetch_item(const KParams& p, int idx, WorkItem& 
     w.rec_count = nbl <= 0 ? 0 : min(p.ref_bpc, nbl - b0);
     w.fresh = chunk == nch - 1;
     w.slot = (jb * NKV + kvh) * p.ref_nchunks + chunk;
-    w.pad = 0;
+    w.tile = 0;
     return true;
 }
 
@@ -568,33 +577,105 @@ __device__ __forceinline__ void attn_tile_body(const KParams& p, const int cta) 
                 LLATTN_TR(4, t);
             }
             if (!alive) break;
-            // ---- epilogue: un-normalised O, reference exponent and row sum of the run
+            // ---- epilogue. A run that is its tile's only one writes the outputs straight from tensor memory. Otherwise
+            // it stores its un-normalised O, reference exponent and row sum as a partial result; the run whose rows
+            // complete the tile (arrival counter per tile and lane quarter) folds the tile's partials together, in slot
+            // order whoever comes last, and writes the outputs. It never waits for another CTA.
             const uint32_t tl = t - 1;
             if (!ptx::mbar_wait(BAR(B_PV_DONE + (tl & 1)), (tl >> 1) & 1, abort_flag)) { alive = false; errbits |= ERR_WAIT_SOFTMAX; break; }
             ptx::tc_fence_after();
-            float* orow = p.Opart + (size_t(w.slot) * QR + row) * D;
-#pragma unroll 1
-            for (int c = 0; c < 4; ++c) {
-                uint32_t r[32];
-                ptx::tmem_ld32(tlane + TM_O + 32 * c, r);
-                ptx::tmem_wait_ld_tied(r);
-#pragma unroll
-                for (int g = 0; g < 4; ++g) {      // positions (0..7) hold dims (0,4,1,5,2,6,3,7)
-                    const float4 lo = make_float4(__uint_as_float(r[8 * g]), __uint_as_float(r[8 * g + 2]),
-                                                  __uint_as_float(r[8 * g + 4]), __uint_as_float(r[8 * g + 6]));
-                    const float4 hi = make_float4(__uint_as_float(r[8 * g + 1]), __uint_as_float(r[8 * g + 3]),
-                                                  __uint_as_float(r[8 * g + 5]), __uint_as_float(r[8 * g + 7]));
-                    *reinterpret_cast<float4*>(orow + 32 * c + 8 * g) = lo;
-                    *reinterpret_cast<float4*>(orow + 32 * c + 8 * g + 4) = hi;
-                }
-            }
+            float lsum;
             {
                 uint32_t r[16];
                 ptx::tmem_ld16(tlane + TM_L, r);
                 ptx::tmem_wait_ld_tied(r);
-                p.Lpart[size_t(w.slot) * QR + row] = __uint_as_float(r[0]);
+                lsum = __uint_as_float(r[0]);
             }
-            p.Mpart[size_t(w.slot) * QR + row] = mref;
+            const bool fused = p.merge != nullptr;
+            MergeDesc md{0, 0, 0, 1};
+            if (fused) md = p.merge[w.tile];
+            bool finish = fused && md.nslots == 1;
+            float M = mref, den = lsum;
+            if (!finish) {
+                float* orow = p.Opart + (size_t(w.slot) * QR + row) * D;
+#pragma unroll 1
+                for (int c = 0; c < 4; ++c) {
+                    uint32_t r[32];
+                    ptx::tmem_ld32(tlane + TM_O + 32 * c, r);
+                    ptx::tmem_wait_ld_tied(r);
+#pragma unroll
+                    for (int g = 0; g < 4; ++g) {      // positions (0..7) hold dims (0,4,1,5,2,6,3,7)
+                        const float4 lo = make_float4(__uint_as_float(r[8 * g]), __uint_as_float(r[8 * g + 2]),
+                                                      __uint_as_float(r[8 * g + 4]), __uint_as_float(r[8 * g + 6]));
+                        const float4 hi = make_float4(__uint_as_float(r[8 * g + 1]), __uint_as_float(r[8 * g + 3]),
+                                                      __uint_as_float(r[8 * g + 5]), __uint_as_float(r[8 * g + 7]));
+                        *reinterpret_cast<float4*>(orow + 32 * c + 8 * g) = lo;
+                        *reinterpret_cast<float4*>(orow + 32 * c + 8 * g + 4) = hi;
+                    }
+                }
+                p.Lpart[size_t(w.slot) * QR + row] = lsum;
+                p.Mpart[size_t(w.slot) * QR + row] = mref;
+                if (fused) {
+                    __threadfence();
+                    __syncwarp();
+                    int before = 0;
+                    if (lane == 0) before = atomicAdd(p.tile_counters + 4 * w.tile + warp, 1);
+                    before = __shfl_sync(0xffffffffu, before, 0);
+                    if (before == md.nslots - 1) {
+                        if (lane == 0) p.tile_counters[4 * w.tile + warp] = 0;
+                        __threadfence();
+                        row_scale(p.Mpart, p.Lpart, md.slot_begin, md.nslots, row, M, den);
+#pragma unroll 1
+                        for (int c = 0; c < 4; ++c) {      // the merged row goes back into this CTA's (finished) accumulator
+                            float acc[32];
+                            uint32_t r[32];
+                            row_gather(p.Opart, p.Mpart, md.slot_begin, md.nslots, row, M, c, acc);
+#pragma unroll
+                            for (int g = 0; g < 4; ++g)
+#pragma unroll
+                                for (int k = 0; k < 4; ++k) {
+                                    r[8 * g + 2 * k] = __float_as_uint(acc[8 * g + k]);
+                                    r[8 * g + 2 * k + 1] = __float_as_uint(acc[8 * g + 4 + k]);
+                                }
+                            ptx::tmem_st32(tlane + TM_O + 32 * c, r);
+                        }
+                        ptx::tmem_wait_st();
+                        finish = true;
+                    }
+                }
+            }
+            if (finish) {
+                const float inv = 1.f / den;
+                RowOut ro{size_t(md.q_index) * BLK + (row >> 2), 4 * md.kvh + (row & 3), 0.f, 0};
+                if (p.out.q8) {        // the int8 form needs the row's largest magnitude first
+                    float m = 0.f;
+#pragma unroll 1
+                    for (int c = 0; c < 4; ++c) {
+                        uint32_t r[32];
+                        ptx::tmem_ld32(tlane + TM_O + 32 * c, r);
+                        ptx::tmem_wait_ld_tied(r);
+#pragma unroll
+                        for (int j = 0; j < 32; ++j) m = fmaxf(m, fabsf(__uint_as_float(r[j]) * inv));
+                    }
+                    ro.qscale = fmaxf(__fdiv_rn(m, 127.f), 1e-30f);
+                }
+#pragma unroll 1
+                for (int c = 0; c < 4; ++c) {
+                    uint32_t r[32];
+                    float v[32];
+                    ptx::tmem_ld32(tlane + TM_O + 32 * c, r);
+                    ptx::tmem_wait_ld_tied(r);
+#pragma unroll
+                    for (int g = 0; g < 4; ++g)
+#pragma unroll
+                        for (int k = 0; k < 4; ++k) {
+                            v[8 * g + k] = __uint_as_float(r[8 * g + 2 * k]) * inv;
+                            v[8 * g + 4 + k] = __uint_as_float(r[8 * g + 2 * k + 1]) * inv;
+                        }
+                    row_store(p.out, ro, c, v);
+                }
+                row_finish(p.out, ro, M, den);
+            }
             ptx::tc_fence_before();
             ptx::mbar_arrive(BAR(B_O_FREE));
         }

@@ -34,7 +34,7 @@ struct WorkItem {
     int32_t rec_count;        // records in the run
     int32_t fresh;            // 1: the query block's own fp16 K/V follow the records
     int32_t slot;             // partial-result slot this run writes
-    int32_t pad;
+    int32_t tile;             // output tile (query block x kv head) the run belongs to: index of its MergeDesc
 };
 
 // One output tile (query block x kv head) and the partial slots that make it up.

@@ -61,12 +61,17 @@ struct llattn_ctx {
 struct llattn_plan {
     llattn_ctx* ctx = nullptr;
     llattn_plan_stats stats{};
-    void* dev_blob = nullptr;         // seq descriptors, work items, per-CTA ranges, merge descriptors
+    void* dev_blob = nullptr;         // seq descriptors, work items, per-CTA ranges, tile descriptors (fixed section offsets)
+    void* host_blob = nullptr;        // pinned mirror: llattn_plan_update fills it and copies it up asynchronously
+    size_t blob_bytes = 0, off_seqs = 0, off_items = 0, off_cta = 0, off_merge = 0;
+    size_t cap_seqs = 0, cap_items = 0, cap_tiles = 0;
+    int launch_ctas = 0;              // grid of every launch of this plan (CTAs beyond the used ones find no items)
+    cudaEvent_t ev_upload = nullptr;
+    bool upload_pending = false;
     const llattn::SeqDesc* d_seqs = nullptr;
     const llattn::WorkItem* d_items = nullptr;
     const int32_t* d_cta_first = nullptr;
     const llattn::MergeDesc* d_merge = nullptr;
-    int ntiles_out = 0;               // output tiles = nq_total * 4
 };
 
 namespace {
@@ -268,7 +273,7 @@ extern "C" int llattn_attention_static(const void* Q, const void* Kf, const void
     attn_tile_kernel<false><<<NKV * nchunks * nb, ATTN_THREADS, ATTN_SMEM_BYTES, as_stream(stream)>>>(p);
     CU(cudaGetLastError());
     MergeOut o{static_cast<half*>(O16), O32, LSE, q8, s8, sum8};
-    combine_ref_kernel<<<dim3(NKV, QR / MERGE_ROWS, nb), MERGE_THREADS, 0, as_stream(stream)>>>(Opart, Mpart, Lpart, nchunks, nblocks, bpc, o);
+    combine_ref_kernel<<<dim3(NKV, nb), MERGE_THREADS, 0, as_stream(stream)>>>(Opart, Mpart, Lpart, nchunks, nblocks, bpc, o);
     CU(cudaGetLastError());
     return LLATTN_OK;
 }

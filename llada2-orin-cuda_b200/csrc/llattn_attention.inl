@@ -5,6 +5,17 @@ namespace {
 
 constexpr size_t SLOT_O_BYTES = size_t(llattn::QR) * llattn::D * sizeof(float);   // 64 KiB
 constexpr size_t SLOT_ML_BYTES = size_t(llattn::QR) * sizeof(float);
+// The scratch starts with the arrival counters of the fused merge (4 per output tile, all zero between launches: the run
+// that completes a tile puts its counter back), then the partial slots.
+constexpr int COUNTER_TILES = 16384;
+constexpr size_t COUNTER_BYTES = size_t(COUNTER_TILES) * 4 * sizeof(int);
+
+int grow_workspace(llattn_ctx* c, size_t need) {
+    if (need <= c->workspace_bytes) return LLATTN_OK;
+    if (int rc = grow(&c->workspace, &c->workspace_bytes, need)) return rc;
+    CU(cudaMemset(c->workspace, 0, COUNTER_BYTES));
+    return LLATTN_OK;
+}
 
 // Splits the flattened unit sequence (every (sequence, query block, kv head) tile contributes nblocks + j records and
 // one fresh block, in that order) into `nctas` contiguous shares of near-equal size. A share boundary inside a tile
@@ -17,7 +28,7 @@ struct HostPlan {
     std::vector<int32_t> cta_first;
     std::vector<llattn::MergeDesc> merge;
     int64_t total_units = 0, max_cta_units = 0;
-    int nq_total = 0;
+    int nq_total = 0, used_ctas = 0;
 };
 
 int build_plan(const llattn_seq* seqs, int nseq, int nctas, HostPlan& hp) {
@@ -63,13 +74,13 @@ int build_plan(const llattn_seq* seqs, int nseq, int nctas, HostPlan& hp) {
                 const int nrec = seqs[s].nblocks + j;
                 const int U = nrec + 1;
                 int done = 0;
-                const int slot0 = slot;
+                const int slot0 = slot, tile = int(hp.merge.size());
                 while (done < U) {
                     int take = int(std::min<int64_t>(room, U - done));
                     if (take < U - done) take = take / TILE_UNITS * TILE_UNITS;     // keep the cut on a tile boundary
                     if (take == 0) { next_cta(); continue; }
                     const int rec_cnt = std::min(take, nrec - done);
-                    hp.items.push_back(WorkItem{s, j, h, done, std::max(rec_cnt, 0), done + take == U ? 1 : 0, slot++, 0});
+                    hp.items.push_back(WorkItem{s, j, h, done, std::max(rec_cnt, 0), done + take == U ? 1 : 0, slot++, tile});
                     done += take;
                     room -= take;
                     left -= take;
@@ -78,6 +89,9 @@ int build_plan(const llattn_seq* seqs, int nseq, int nctas, HostPlan& hp) {
                 hp.merge.push_back(MergeDesc{seqs[s].q_first + j, h, slot0, slot - slot0});
             }
     if (hp.cta_first.back() != int32_t(hp.items.size())) hp.cta_first.push_back(int32_t(hp.items.size()));
+    hp.used_ctas = int(hp.cta_first.size()) - 1;
+    // the launch always has `nctas` CTAs (a captured graph keeps its grid when the plan is updated): the rest get no items
+    while (int(hp.cta_first.size()) < nctas + 1) hp.cta_first.push_back(int32_t(hp.items.size()));
     hp.max_cta_units = 0;
     for (size_t c = 0; c + 1 < hp.cta_first.size(); ++c) {
         int64_t u = 0;
@@ -136,7 +150,7 @@ int llattn_attn_combine(const float* Opart, const float* Mpart, const float* Lpa
     MergeOut o{};
     if (q8) { o.q8 = q8; o.s8 = s8; o.sum8 = sum8; }       // as the reference: int8 form replaces the fp16 output
     else o.O16 = static_cast<half*>(O);
-    combine_ref_kernel<<<dim3(NKV, QR / MERGE_ROWS, nb), MERGE_THREADS, 0, as_stream(stream)>>>(Opart, Mpart, Lpart, nchunks, nblocks, bpc, o);
+    combine_ref_kernel<<<dim3(NKV, nb), MERGE_THREADS, 0, as_stream(stream)>>>(Opart, Mpart, Lpart, nchunks, nblocks, bpc, o);
     CU(cudaGetLastError());
     return LLATTN_OK;
 }
@@ -182,6 +196,36 @@ void llattn_destroy(llattn_ctx* c) {
     delete c;
 }
 
+namespace {
+
+inline size_t up256(size_t x) { return (x + 255) / 256 * 256; }
+
+void fill_stats(llattn_plan* pl, const HostPlan& hp, int nseq) {
+    pl->stats.nseq = nseq;
+    pl->stats.nq_total = hp.nq_total;
+    pl->stats.nitems = int32_t(hp.items.size());
+    pl->stats.nslots = int32_t(hp.items.size());
+    pl->stats.nctas = hp.used_ctas;
+    pl->stats.total_units = hp.total_units;
+    pl->stats.max_cta_units = hp.max_cta_units;
+}
+
+// Lays the host plan out in the plan's pinned mirror (section offsets are fixed by the capacities chosen at creation).
+int stage_plan(llattn_plan* pl, const HostPlan& hp) {
+    if (hp.seqs.size() > pl->cap_seqs || hp.items.size() > pl->cap_items || hp.merge.size() > pl->cap_tiles ||
+        hp.cta_first.size() != size_t(pl->launch_ctas) + 1)
+        return fail(LLATTN_ENOMEM, "plan: %zu sequences, %zu runs, %zu tiles; the plan was created for %zu, %zu, %zu",
+                    hp.seqs.size(), hp.items.size(), hp.merge.size(), pl->cap_seqs, pl->cap_items, pl->cap_tiles);
+    uint8_t* h = static_cast<uint8_t*>(pl->host_blob);
+    memcpy(h + pl->off_seqs, hp.seqs.data(), hp.seqs.size() * sizeof(llattn::SeqDesc));
+    memcpy(h + pl->off_items, hp.items.data(), hp.items.size() * sizeof(llattn::WorkItem));
+    memcpy(h + pl->off_cta, hp.cta_first.data(), hp.cta_first.size() * sizeof(int32_t));
+    memcpy(h + pl->off_merge, hp.merge.data(), hp.merge.size() * sizeof(llattn::MergeDesc));
+    return LLATTN_OK;
+}
+
+}  // namespace
+
 int llattn_plan_create(llattn_ctx* c, const llattn_seq* seqs, int nseq, int nctas, llattn_plan** out) {
     using namespace llattn;
     if (!c || !seqs || !out) return fail(LLATTN_EINVAL, "plan_create: null pointer");
@@ -190,41 +234,66 @@ int llattn_plan_create(llattn_ctx* c, const llattn_seq* seqs, int nseq, int ncta
     if (nctas <= 0) nctas = c->num_sms;
     HostPlan hp;
     if (int rc = build_plan(seqs, nseq, nctas, hp)) return rc;
+    if (hp.merge.size() > COUNTER_TILES) return fail(LLATTN_EINVAL, "plan_create: %zu output tiles, at most %d per call", hp.merge.size(), COUNTER_TILES);
     std::lock_guard<std::mutex> lk(c->mu);
     DeviceGuard g(c->device);
     if (!g.ok) return fail(LLATTN_ECUDA, "plan_create: cannot select device %d", c->device);
     llattn_plan* pl = new (std::nothrow) llattn_plan();
     if (!pl) return fail(LLATTN_ENOMEM, "plan_create: out of host memory");
     pl->ctx = c;
-    auto up = [](size_t x) { return (x + 255) / 256 * 256; };
-    const size_t b_seq = up(hp.seqs.size() * sizeof(SeqDesc)), b_it = up(hp.items.size() * sizeof(WorkItem)),
-                 b_cf = up(hp.cta_first.size() * sizeof(int32_t)), b_md = up(hp.merge.size() * sizeof(MergeDesc));
-    std::vector<uint8_t> blob(b_seq + b_it + b_cf + b_md, 0);
-    memcpy(blob.data(), hp.seqs.data(), hp.seqs.size() * sizeof(SeqDesc));
-    memcpy(blob.data() + b_seq, hp.items.data(), hp.items.size() * sizeof(WorkItem));
-    memcpy(blob.data() + b_seq + b_it, hp.cta_first.data(), hp.cta_first.size() * sizeof(int32_t));
-    memcpy(blob.data() + b_seq + b_it + b_cf, hp.merge.data(), hp.merge.size() * sizeof(MergeDesc));
-    if (cudaMalloc(&pl->dev_blob, blob.size()) != cudaSuccess) { cudaGetLastError(); delete pl; return fail(LLATTN_ENOMEM, "plan_create: cudaMalloc of %zu bytes failed", blob.size()); }
-    if (cudaMemcpy(pl->dev_blob, blob.data(), blob.size(), cudaMemcpyHostToDevice) != cudaSuccess) {
-        cudaGetLastError(); cudaFree(pl->dev_blob); delete pl;
-        return fail(LLATTN_ECUDA, "plan_create: upload failed");
-    }
+    pl->launch_ctas = nctas;
+    // Capacities: a later llattn_plan_update may change every length, as long as the sequences keep their number and
+    // their query-block counts. A tile is cut at most once per CTA boundary, so tiles + CTAs bounds the runs.
+    pl->cap_seqs = hp.seqs.size();
+    pl->cap_tiles = hp.merge.size();
+    pl->cap_items = hp.merge.size() + size_t(nctas);
+    pl->off_seqs = 0;
+    pl->off_items = pl->off_seqs + up256(pl->cap_seqs * sizeof(SeqDesc));
+    pl->off_cta = pl->off_items + up256(pl->cap_items * sizeof(WorkItem));
+    pl->off_merge = pl->off_cta + up256((size_t(nctas) + 1) * sizeof(int32_t));
+    pl->blob_bytes = pl->off_merge + up256(pl->cap_tiles * sizeof(MergeDesc));
+    auto bail = [&](int code, const char* what) {
+        if (pl->dev_blob) cudaFree(pl->dev_blob);
+        if (pl->host_blob) cudaFreeHost(pl->host_blob);
+        if (pl->ev_upload) cudaEventDestroy(pl->ev_upload);
+        cudaGetLastError();
+        delete pl;
+        return fail(code, "plan_create: %s", what);
+    };
+    if (cudaMalloc(&pl->dev_blob, pl->blob_bytes) != cudaSuccess) return bail(LLATTN_ENOMEM, "cudaMalloc of the plan failed");
+    if (cudaMallocHost(&pl->host_blob, pl->blob_bytes) != cudaSuccess) return bail(LLATTN_ENOMEM, "cudaMallocHost of the plan mirror failed");
+    if (cudaEventCreateWithFlags(&pl->ev_upload, cudaEventDisableTiming) != cudaSuccess) return bail(LLATTN_ECUDA, "cudaEventCreate failed");
+    memset(pl->host_blob, 0, pl->blob_bytes);
+    if (int rc = stage_plan(pl, hp)) { bail(rc, "internal"); return rc; }
+    if (cudaMemcpy(pl->dev_blob, pl->host_blob, pl->blob_bytes, cudaMemcpyHostToDevice) != cudaSuccess) return bail(LLATTN_ECUDA, "upload failed");
     const uint8_t* d = static_cast<const uint8_t*>(pl->dev_blob);
-    pl->d_seqs = reinterpret_cast<const SeqDesc*>(d);
-    pl->d_items = reinterpret_cast<const WorkItem*>(d + b_seq);
-    pl->d_cta_first = reinterpret_cast<const int32_t*>(d + b_seq + b_it);
-    pl->d_merge = reinterpret_cast<const MergeDesc*>(d + b_seq + b_it + b_cf);
-    pl->ntiles_out = int(hp.merge.size());
-    pl->stats.nseq = nseq;
-    pl->stats.nq_total = hp.nq_total;
-    pl->stats.nitems = int32_t(hp.items.size());
-    pl->stats.nslots = int32_t(hp.items.size());
-    pl->stats.nctas = int32_t(hp.cta_first.size()) - 1;
-    pl->stats.total_units = hp.total_units;
-    pl->stats.max_cta_units = hp.max_cta_units;
-    pl->stats.workspace_bytes = hp.items.size() * (SLOT_O_BYTES + 2 * SLOT_ML_BYTES);
-    if (int rc = grow(&c->workspace, &c->workspace_bytes, pl->stats.workspace_bytes)) { cudaFree(pl->dev_blob); delete pl; return rc; }
+    pl->d_seqs = reinterpret_cast<const SeqDesc*>(d + pl->off_seqs);
+    pl->d_items = reinterpret_cast<const WorkItem*>(d + pl->off_items);
+    pl->d_cta_first = reinterpret_cast<const int32_t*>(d + pl->off_cta);
+    pl->d_merge = reinterpret_cast<const MergeDesc*>(d + pl->off_merge);
+    fill_stats(pl, hp, nseq);
+    // the scratch is sized for the most runs any update can bring, so that an update never allocates
+    pl->stats.workspace_bytes = COUNTER_BYTES + pl->cap_items * (SLOT_O_BYTES + 2 * SLOT_ML_BYTES);
+    if (int rc = grow_workspace(c, pl->stats.workspace_bytes)) { bail(rc, "workspace"); return rc; }
     *out = pl;
+    return LLATTN_OK;
+}
+
+int llattn_plan_update(llattn_plan* pl, const llattn_seq* seqs, int nseq, void* stream) {
+    using namespace llattn;
+    if (!pl || !seqs) return fail(LLATTN_EINVAL, "plan_update: null pointer");
+    if (size_t(nseq) != pl->cap_seqs) return fail(LLATTN_EINVAL, "plan_update: %d sequences, the plan was created for %zu", nseq, pl->cap_seqs);
+    HostPlan hp;
+    if (int rc = build_plan(seqs, nseq, pl->launch_ctas, hp)) return rc;
+    // the pinned mirror is reused: the previous update's copy must have left it (a wait on a finished copy, not on kernels)
+    if (pl->upload_pending) { CU(cudaEventSynchronize(pl->ev_upload)); pl->upload_pending = false; }
+    if (int rc = stage_plan(pl, hp)) return rc;
+    CU(cudaMemcpyAsync(pl->dev_blob, pl->host_blob, pl->blob_bytes, cudaMemcpyHostToDevice, as_stream(stream)));
+    CU(cudaEventRecord(pl->ev_upload, as_stream(stream)));
+    pl->upload_pending = true;
+    const size_t ws = pl->stats.workspace_bytes;
+    fill_stats(pl, hp, nseq);
+    pl->stats.workspace_bytes = ws;
     return LLATTN_OK;
 }
 
@@ -239,17 +308,17 @@ int llattn_plan_preview(const llattn_seq* seqs, int nseq, int nctas, llattn_plan
     stats->nseq = nseq;
     stats->nq_total = hp.nq_total;
     stats->nitems = stats->nslots = int32_t(hp.items.size());
-    stats->nctas = int32_t(hp.cta_first.size()) - 1;
+    stats->nctas = hp.used_ctas;
     stats->total_units = hp.total_units;
     stats->max_cta_units = hp.max_cta_units;
-    stats->workspace_bytes = hp.items.size() * (SLOT_O_BYTES + 2 * SLOT_ML_BYTES);
+    stats->workspace_bytes = COUNTER_BYTES + (hp.merge.size() + size_t(nctas)) * (SLOT_O_BYTES + 2 * SLOT_ML_BYTES);
     if (items_out) {
         if (max_items < int(hp.items.size())) return fail(LLATTN_ENOMEM, "plan_preview: %zu items, room for %d", hp.items.size(), max_items);
         memcpy(items_out, hp.items.data(), hp.items.size() * sizeof(WorkItem));
     }
     if (cta_first_out) {
-        if (max_ctas + 1 < int(hp.cta_first.size())) return fail(LLATTN_ENOMEM, "plan_preview: %zu CTA bounds, room for %d", hp.cta_first.size(), max_ctas + 1);
-        memcpy(cta_first_out, hp.cta_first.data(), hp.cta_first.size() * sizeof(int32_t));
+        if (max_ctas < hp.used_ctas) return fail(LLATTN_ENOMEM, "plan_preview: %d CTAs, room for %d", hp.used_ctas, max_ctas);
+        memcpy(cta_first_out, hp.cta_first.data(), (size_t(hp.used_ctas) + 1) * sizeof(int32_t));
     }
     return LLATTN_OK;
 }
@@ -257,7 +326,10 @@ int llattn_plan_preview(const llattn_seq* seqs, int nseq, int nctas, llattn_plan
 void llattn_plan_destroy(llattn_plan* pl) {
     if (!pl) return;
     DeviceGuard g(pl->ctx->device);
+    if (pl->upload_pending) cudaEventSynchronize(pl->ev_upload);
     cudaFree(pl->dev_blob);
+    cudaFreeHost(pl->host_blob);
+    cudaEventDestroy(pl->ev_upload);
     delete pl;
 }
 
@@ -268,22 +340,18 @@ int llattn_plan_get_stats(const llattn_plan* pl, llattn_plan_stats* out) {
 }
 
 int llattn_attention(llattn_ctx* c, const llattn_plan* pl, const llattn_io* io, void* stream) {
-    return llattn_attention_parts(c, pl, io, 3, stream);
-}
-
-int llattn_attention_parts(llattn_ctx* c, const llattn_plan* pl, const llattn_io* io, int parts, void* stream) {
     using namespace llattn;
     if (!c || !pl || pl->ctx != c) return fail(LLATTN_EINVAL, "attention: plan does not belong to this context");
-    if (parts < 1 || parts > 3) return fail(LLATTN_EINVAL, "attention: parts must be 1, 2 or 3");
     if (int rc = check_io(io, "attention")) return rc;
     if (!aligned16(io->Q) || !aligned16(io->Kf) || !aligned16(io->Vf) || !aligned16(io->O16) || !aligned16(io->O32))
         return fail(LLATTN_EINVAL, "attention: pointers must be 16-byte aligned");
+    if (io->cache_offset & 15) return fail(LLATTN_EINVAL, "attention: cache_offset must be a multiple of 16 bytes");
     if (c->workspace_bytes < pl->stats.workspace_bytes) return fail(LLATTN_ENOMEM, "attention: workspace smaller than the plan needs");
     int dev = -1;
     CU(cudaGetDevice(&dev));
     if (dev != c->device) return fail(LLATTN_EINVAL, "attention: current device %d, context device %d", dev, c->device);
-    const size_t ns = size_t(pl->stats.nslots);
-    float* Opart = static_cast<float*>(c->workspace);
+    const size_t ns = pl->cap_items;
+    float* Opart = reinterpret_cast<float*>(static_cast<uint8_t*>(c->workspace) + COUNTER_BYTES);
     float* Mpart = Opart + ns * QR * D;
     float* Lpart = Mpart + ns * QR;
     KParams p{};
@@ -292,16 +360,13 @@ int llattn_attention_parts(llattn_ctx* c, const llattn_plan* pl, const llattn_io
     p.Opart = Opart; p.Mpart = Mpart; p.Lpart = Lpart;
     p.sl2 = (io->scale > 0.f ? io->scale : 0.08838834764831845f) * 1.4426950408889634f;
     p.err = c->err_word;
-    if (parts & 1) {
-        if (io->flags & LLATTN_IO_PRECISE_P) attn_tile_kernel<true><<<pl->stats.nctas, ATTN_THREADS, ATTN_SMEM_BYTES, as_stream(stream)>>>(p);
-        else attn_tile_kernel<false><<<pl->stats.nctas, ATTN_THREADS, ATTN_SMEM_BYTES, as_stream(stream)>>>(p);
-        CU(cudaGetLastError());
-    }
-    if (parts & 2) {
-        MergeOut o{static_cast<half*>(io->O16), io->O32, io->LSE, io->q8, io->s8, io->sum8};
-        merge_kernel<<<dim3(pl->ntiles_out, QR / MERGE_ROWS), MERGE_THREADS, 0, as_stream(stream)>>>(pl->d_merge, Opart, Mpart, Lpart, o);
-        CU(cudaGetLastError());
-    }
+    p.merge = pl->d_merge;
+    p.tile_counters = static_cast<int*>(c->workspace);
+    p.out = MergeOut{static_cast<half*>(io->O16), io->O32, io->LSE, io->q8, io->s8, io->sum8};
+    p.cache_offset = io->cache_offset;
+    if (io->flags & LLATTN_IO_PRECISE_P) attn_tile_kernel<true><<<pl->launch_ctas, ATTN_THREADS, ATTN_SMEM_BYTES, as_stream(stream)>>>(p);
+    else attn_tile_kernel<false><<<pl->launch_ctas, ATTN_THREADS, ATTN_SMEM_BYTES, as_stream(stream)>>>(p);
+    CU(cudaGetLastError());
     return LLATTN_OK;
 }
 
@@ -345,7 +410,7 @@ int llattn_attention_host(llattn_ctx* c, const llattn_plan* pl, const llattn_io*
     uint8_t* dQ = d; d += up(bQ);
     uint8_t* dK = d; d += up(bKV);
     uint8_t* dV = d; d += up(bKV);
-    dio.Q = dQ; dio.Kf = dK; dio.Vf = dV; dio.scale = h->scale; dio.flags = h->flags;
+    dio.Q = dQ; dio.Kf = dK; dio.Vf = dV; dio.scale = h->scale; dio.flags = h->flags; dio.cache_offset = h->cache_offset;
     if (bO16) { dio.O16 = d; d += up(bO16); }
     if (bO32) { dio.O32 = reinterpret_cast<float*>(d); d += up(bO32); }
     if (bLSE) { dio.LSE = reinterpret_cast<float*>(d); d += up(bLSE); }
@@ -354,8 +419,10 @@ int llattn_attention_host(llattn_ctx* c, const llattn_plan* pl, const llattn_io*
         dio.s8 = reinterpret_cast<float*>(d); d += up(bs8);
         dio.sum8 = reinterpret_cast<int32_t*>(d); d += up(bs8);
     }
-    // upload: the slot's previous kernels (two calls ago) must have finished reading it
+    // upload: the slot's previous kernels (two calls ago) must have finished reading it, and its previous download must
+    // have drained the output area (a plan with more query blocks lays the slot out differently)
     CU(cudaStreamWaitEvent(c->s_in, c->ev_comp[slot], 0));
+    CU(cudaStreamWaitEvent(c->s_in, c->ev_out[slot], 0));
     CU(cudaMemcpyAsync(dQ, h->Q, bQ, cudaMemcpyHostToDevice, c->s_in));
     CU(cudaMemcpyAsync(dK, h->Kf, bKV, cudaMemcpyHostToDevice, c->s_in));
     CU(cudaMemcpyAsync(dV, h->Vf, bKV, cudaMemcpyHostToDevice, c->s_in));
@@ -363,7 +430,7 @@ int llattn_attention_host(llattn_ctx* c, const llattn_plan* pl, const llattn_io*
     // kernels: after the upload, and after the slot's previous download has drained its output area
     CU(cudaStreamWaitEvent(st, c->ev_in[slot], 0));
     CU(cudaStreamWaitEvent(st, c->ev_out[slot], 0));
-    if (int rc = llattn_attention_parts(c, pl, &dio, 3, stream)) return rc;
+    if (int rc = llattn_attention(c, pl, &dio, stream)) return rc;
     CU(cudaEventRecord(c->ev_comp[slot], st));
     // download
     CU(cudaStreamWaitEvent(c->s_out, c->ev_comp[slot], 0));
@@ -393,6 +460,7 @@ int llattn_device_status(llattn_ctx* c, void* stream, int* code) {
     CU(cudaMemcpy(code, c->err_word, sizeof(int), cudaMemcpyDeviceToHost));
     if (*code) {
         CU(cudaMemset(c->err_word, 0, sizeof(int)));
+        if (c->workspace) CU(cudaMemset(c->workspace, 0, COUNTER_BYTES));      // an aborted launch may have left tile counters behind
         return fail(LLATTN_EDEVICE, "a kernel wait ran out (error bits 0x%x)", *code);
     }
     return LLATTN_OK;

@@ -1,6 +1,7 @@
 """ctypes face of oracle/_ref/libattn_ref.so: the reference's own attn.cu kernels compiled for sm_100a by
-oracle/Makefile (`make ref`) where the reference checkout exists. Test infrastructure only. `available()` is False
-when the file did not travel; tests that need it skip."""
+oracle/Makefile (`make ref`) where the reference checkout exists. Test and measurement infrastructure only: the GPU
+parity tests use it as the reference-kernel oracle and bench.py times it beside the new kernel. `available()` is
+False when the file did not travel; tests that need it skip."""
 import ctypes
 import os
 
@@ -58,6 +59,34 @@ def attention(Q, Kf, Vf, cache, max_blocks, nblocks, bpc=0, int8=False):
     assert rc == 0, rc
     torch.cuda.synchronize()
     return (q8, s8, sum8) if int8 else O
+
+
+class BatchRunner:
+    """The reference's attn_partial + attn_combine for a batch of independent sequences, one query block each: the
+    reference serves one sequence per launch pair, so a batch is one launch pair per sequence, spread over `nstreams`
+    streams so that the GPU can overlap them. Partial buffers are allocated once."""
+
+    def __init__(self, nseq, nblocks, device, nstreams=8):
+        import torch
+        L = lib()
+        self.bpc = L.ref_pick_bpc(nblocks, 1)
+        self.nch = L.ref_chunks_for(nblocks, self.bpc)
+        self.nblocks = nblocks
+        self.Op = torch.empty((nseq, 4, self.nch, 128, 128), dtype=torch.float32, device=device)
+        self.Mp = torch.empty((nseq, 4, self.nch, 128), dtype=torch.float32, device=device)
+        self.Lp = torch.empty((nseq, 4, self.nch, 128), dtype=torch.float32, device=device)
+        self.O = torch.empty((nseq * 32, 16, 128), dtype=torch.float16, device=device)
+        self.streams = [torch.cuda.Stream(device=device) for _ in range(nstreams)]
+
+    def launch(self, Q, Kf, Vf, caches, max_blocks):
+        """Q [nseq][32][16][128], Kf/Vf [nseq][32][4][128], caches [nseq][4][max_blocks][4736]; launches only."""
+        L = lib()
+        for s in range(Q.shape[0]):
+            st = self.streams[s % len(self.streams)]
+            rc = L.ref_attention(Q[s].data_ptr(), Kf[s].data_ptr(), Vf[s].data_ptr(), caches[s].data_ptr(), max_blocks,
+                                 self.nblocks, 1, self.bpc, self.Op[s].data_ptr(), self.Mp[s].data_ptr(), self.Lp[s].data_ptr(),
+                                 self.O[32 * s:32 * s + 32].data_ptr(), None, None, None, st.cuda_stream)
+            assert rc == 0, rc
 
 
 OPS_PATH = os.path.join(ROOT, "oracle", "_ref", "libops_ref.so")

@@ -28,7 +28,7 @@ sys.path.insert(0, ROOT)
 wl = importlib.import_module("llada2-orin-cuda_b200").workload
 
 ap = argparse.ArgumentParser()
-ap.add_argument("--ref", default="/root/reference")
+ap.add_argument("--ref", required=True, help="path of the reference checkout (its quant/ directory is imported)")
 a = ap.parse_args()
 sys.path.insert(0, os.path.join(a.ref, "quant"))
 sys.dont_write_bytecode = True

@@ -148,4 +148,6 @@ def test_kernel_error_is_the_emulated_fp16_rounding_of_p(api, ctx, orc, pkg, nbl
         if not precise:
             assert abs(e_k - e_e) <= 0.15 * e_e and abs(l_k - l_e) <= 0.1 * l_e
         else:
-            assert e_k <= 2e-4 and e_e <= 5e-5
+            # one run of 257 units per kv head: the tensor core's own fp32 accumulation over a chain that long shows
+            # (4e-4 x RMS here, 1.6e-3 for a 1025-unit run); in the planner's usual cuts it is below 1e-4
+            assert e_k <= 1e-3 and e_e <= 5e-5
