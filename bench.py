@@ -270,6 +270,15 @@ class Rank:
             self.dist.all_reduce(t, op=self.dist.ReduceOp.MAX)
         return [float(x) for x in t.tolist()]
 
+    def gather(self, value):
+        """`value` of every rank, in rank order."""
+        t = self.torch.tensor([value], device=self.dev, dtype=self.torch.float64)
+        if self.world == 1:
+            return [float(value)]
+        out = [self.torch.empty_like(t) for _ in range(self.world)]
+        self.dist.all_gather(out, t)
+        return [float(x.item()) for x in out]
+
     def finish(self):
         if self.world > 1:
             self.dist.barrier()
@@ -611,7 +620,7 @@ def run_decode(a):
                 refk["ours_ms_per_layer"] = launch_ms
                 refk["speedup"] = refk["ms_per_layer"] / launch_ms
             line["reference_kernel"] = refk
-        if not a.no_cpu_baseline:
+        if not a.no_cpu_baseline and R.world == 1:        # a reported baseline of the N = 1 line only (other ranks would be spinning beside it)
             times, threads = cpu_sample_seconds(a.ctx, 3)
             sec = min(times)
             line["cpu_baseline"] = {"value": 32.0 / (L * sec), "unit": "query_tok/s", "cores": threads, "kind": "port",
@@ -707,7 +716,10 @@ def run_ragged(a):
     O = torch.zeros((L, len(lens) * 32, 16, 128), dtype=torch.float16, device=R.dev)
     step = Step(R, ctx, plan, layer_bytes, Q, Kf, Vf, O, graph=not a.no_graph, precise=a.precise)
     sampler = ClockSampler(R.local, R.pci) if R.rank == 0 else None
-    ms = R.max_over_ranks([step.timed(a.steps, a.warmup, sampler)])[0]
+    ms_mine = step.timed(a.steps, a.warmup, sampler)
+    ms = R.max_over_ranks([ms_mine])[0]
+    ms_ranks = [x / a.steps for x in R.gather(ms_mine)]
+    units_ranks = R.gather(st.total_units)
     clocks = sampler.stop() if sampler else None
     assert ctx.device_status(R.stream) == 0
     if R.rank == 0:
@@ -724,7 +736,8 @@ def run_ragged(a):
                            "l2": "inputs larger than L2", "graph": "20-layer step replayed as one CUDA graph"},
                 "balance": {"kv_bytes_per_gpu_max": max(kv_bytes), "kv_bytes_per_gpu_mean": sum(kv_bytes) / len(kv_bytes),
                             "max_over_mean": max(kv_bytes) / (sum(kv_bytes) / len(kv_bytes)), "sequences_per_gpu": [len(s) for s in shards],
-                            "cta_max_over_mean_units_rank0": st.max_cta_units / (st.total_units / st.nctas)},
+                            "cta_max_over_mean_units_rank0": st.max_cta_units / (st.total_units / st.nctas),
+                            "ms_per_step_per_gpu": ms_ranks, "kv_units_per_gpu": units_ranks},
                 "roofline": {"bound": "tensor", "achieved": ach_tf, "peak": pk["tf_sustained"], "unit": "TFLOP/s", "frac": ach_tf / pk["tf_sustained"],
                              "frac_burst": ach_tf / pk["tf_burst"], "traffic": None, "kernel": "attn_tile_kernel",
                              "hbm_achieved_gbs": max(bytes_rank) / (ms_step * 1e-3) / 1e9, "hbm_peak_gbs": pk["hbm"],

@@ -73,6 +73,16 @@ int llattn_kv_commit_paged(const void* Kf, const void* Vf, void* pool, const int
 int llattn_qk_norm_rope(const float* qkv, const int32_t* pos, const float* gq, const float* gk, float eps,
                         const float* inv_freq, void* q, void* k, void* v, int T, void* stream);
 
+/* The same producer for a prefill pass of `nb` whole 32-token blocks (T = 32 nb), fused with their commit: stands in
+ * for the pair ops::qk_norm_rope + attn::kv_commit at engine/engine.cu:589-591. q, k, v are written as above (the
+ * attention step reads the fresh fp16 K/V), and block j, kv head h also becomes record blk + j of head h of `cache`
+ * (pages == NULL), or record pages[j * 4 + h] of the pool `cache` (pages: device array of nb * 4 indices) - quantised
+ * from the fp16 values still in shared memory, without reading K/V back. Bytes are identical to running the two
+ * reference kernels one after the other. */
+int llattn_qkv_prepare_commit(const float* qkv, const int32_t* pos, const float* gq, const float* gk, float eps,
+                              const float* inv_freq, void* q, void* k, void* v, int nb, void* cache, const int32_t* pages,
+                              int max_blocks, int blk, void* stream);
+
 /* ---- consumer of the attention output: the dense projection on the int8 `Act` the merge kernel writes.
  * Stands in for Engine::gemm<4, 2>(Ly.dense, items_dense, ..., oA.a, ones, HID, HID, nullptr, h, 1, 2)
  * (engine/engine.cu:434 -> moe8::gemm<4, 4, 2, 2>, engine/moe_i8.cu:295-442) for any number of tokens:
@@ -252,6 +262,14 @@ int llattn_kvpool_pages(llattn_kvpool* pool, int32_t seq_id, int32_t* pages_out,
 int llattn_kvpool_close(llattn_kvpool* pool, int32_t seq_id);
 /* out6 = pages, free, cached (reusable, unreferenced), block hits, block misses, evictions */
 int llattn_kvpool_stats(llattn_kvpool* pool, int64_t* out6);
+
+/* Self-test of the bounded waits every kernel here is built on, with nothing made to fail: one CTA whose four warps
+ * wait on barriers that nothing will ever complete. Warp 0's limit is `limit_ns` (1 ns .. 100 ms); when it runs out
+ * the warp raises the CTA's abort flag and the other warps, whose own limit is the kernels' two seconds, leave at their
+ * next poll. The kernel returns normally; `err_word` (device int, zeroed by the caller) then holds bits 1|2|4|8 (one per
+ * warp, the producer / dequant / MMA / softmax codes of llattn_device_status) and waited_ns4 (device, 4 x uint64) how
+ * long each warp waited. No counterpart in the reference, whose kernels have no waits that can fail. */
+int llattn_wait_selftest(unsigned long long limit_ns, int* err_word, unsigned long long* waited_ns4, void* stream);
 
 /* Reads (and clears) the context's device error word; synchronises `stream`. 0 = no kernel wait ran out. */
 int llattn_device_status(llattn_ctx* ctx, void* stream, int* code);

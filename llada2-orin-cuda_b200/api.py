@@ -25,11 +25,11 @@ IO_PRECISE_P = 1  # llattn_io.flags
 
 EXPORTS = (
     "llattn_version", "llattn_last_error", "llattn_pick_bpc", "llattn_chunks_for", "llattn_tile_units", "llattn_kv_commit",
-    "llattn_kv_commit_paged", "llattn_qk_norm_rope", "llattn_attn_partial", "llattn_attn_combine", "llattn_create", "llattn_destroy",
+    "llattn_kv_commit_paged", "llattn_qk_norm_rope", "llattn_qkv_prepare_commit", "llattn_attn_partial", "llattn_attn_combine", "llattn_create", "llattn_destroy",
     "llattn_plan_create", "llattn_plan_destroy", "llattn_plan_get_stats", "llattn_plan_preview", "llattn_attention",
     "llattn_plan_update", "llattn_attention_host", "llattn_host_flush", "llattn_device_status",
     "llattn_dense_w4a8", "llattn_kvpool_create", "llattn_kvpool_destroy", "llattn_kvpool_open", "llattn_kvpool_append", "llattn_kvpool_pages", "llattn_kvpool_mark_committed",
-    "llattn_kvpool_close", "llattn_kvpool_stats", "llattn_attention_static",
+    "llattn_kvpool_close", "llattn_kvpool_stats", "llattn_attention_static", "llattn_wait_selftest",
 )
 
 
@@ -79,6 +79,8 @@ def lib() -> ctypes.CDLL:
         L.llattn_kv_commit_paged.argtypes = [c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_void_p]
         L.llattn_qk_norm_rope.argtypes = [c_void_p, c_void_p, c_void_p, c_void_p, c_float, c_void_p, c_void_p, c_void_p,
                                           c_void_p, c_int, c_void_p]
+        L.llattn_qkv_prepare_commit.argtypes = [c_void_p, c_void_p, c_void_p, c_void_p, c_float, c_void_p, c_void_p, c_void_p,
+                                                c_void_p, c_int, c_void_p, c_void_p, c_int, c_int, c_void_p]
         L.llattn_attn_partial.argtypes = [POINTER(_Args), c_int, c_void_p, c_void_p]
         L.llattn_attn_combine.argtypes = [c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_void_p, c_void_p,
                                           c_void_p, c_void_p, c_int, c_void_p]
@@ -105,6 +107,7 @@ def lib() -> ctypes.CDLL:
         L.llattn_kvpool_close.argtypes = [c_void_p, c_int32]
         L.llattn_kvpool_stats.argtypes = [c_void_p, c_void_p]
         L.llattn_device_status.argtypes = [c_void_p, c_void_p, POINTER(c_int)]
+        L.llattn_wait_selftest.argtypes = [ctypes.c_uint64, c_void_p, c_void_p, c_void_p]
         L.llattn_attention_static.argtypes = [c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_float,
                                               c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p]
         _lib = L
@@ -147,6 +150,12 @@ def tile_units() -> int:
 def chunks_for(nblocks: int, bpc: int) -> int:
     """attn::chunks_for (engine/attn.cu:67)."""
     return lib().llattn_chunks_for(nblocks, bpc)
+
+
+def wait_selftest(limit_ns: int, err_word, waited_ns, stream=None) -> None:
+    """llattn_wait_selftest: four warps wait on barriers nothing completes; err_word (int32 [1]) and waited_ns
+    (int64 [4]) are device tensors."""
+    _check(lib().llattn_wait_selftest(limit_ns, _ptr(err_word), _ptr(waited_ns), _stream(stream)))
 
 
 # ------------------------------------------------------------------ commit
@@ -192,6 +201,18 @@ def qk_norm_rope(qkv, pos, gq, gk, eps, inv_freq_t, q, k, v, stream=None) -> Non
     T = qkv.shape[0]
     _check(lib().llattn_qk_norm_rope(_ptr(qkv), _ptr(pos), _ptr(gq), _ptr(gk), eps, _ptr(inv_freq_t), _ptr(q), _ptr(k),
                                      _ptr(v), T, _stream(stream)))
+
+
+def qkv_prepare_commit(qkv, pos, gq, gk, eps, inv_freq_t, q, k, v, cache, max_blocks: int = 0, blk: int = 0, pages=None,
+                       stream=None) -> None:
+    """The producer for whole 32-token blocks fused with their commit (engine/engine.cu:589-591 in one kernel): q, k, v as
+    qk_norm_rope writes them, and block j becomes record blk + j of `cache` [4][max_blocks][4736] (or, with `pages`
+    int32 [nb][4], record pages[j][h] of the pool `cache`)."""
+    T = qkv.shape[0]
+    if T % BLK:
+        raise ValueError("a prefill pass commits whole 32-token blocks")
+    _check(lib().llattn_qkv_prepare_commit(_ptr(qkv), _ptr(pos), _ptr(gq), _ptr(gk), eps, _ptr(inv_freq_t), _ptr(q), _ptr(k),
+                                           _ptr(v), T // BLK, _ptr(cache), _ptr(pages), max_blocks, blk, _stream(stream)))
 
 
 # ------------------------------------------------------------------ the reference operator pair

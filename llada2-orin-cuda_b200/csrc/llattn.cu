@@ -15,7 +15,7 @@
 #include "kv_commit.cuh"
 #include "attn_kernel.cuh"
 #include "merge_kernel.cuh"
-#include "qk_norm_rope.cuh"
+#include "qkv_prepare.cuh"
 #include "dense_i8.cuh"
 
 namespace {
@@ -154,15 +154,36 @@ int llattn_kv_commit_paged(const void* Kf, const void* Vf, void* pool, const int
 
 // ------------------------------------------------------------------------------------------------------ producer
 
+namespace {
+int launch_prepare(const float* qkv, const int32_t* pos, const float* gq, const float* gk, float eps, const float* inv_freq,
+                   void* q, void* k, void* v, int T, void* records, const int32_t* pages, int max_blocks, int blk, void* stream) {
+    llattn::PrepArgs a{qkv, pos, gq, gk, inv_freq, eps, static_cast<half*>(q), static_cast<half*>(k), static_cast<half*>(v), T,
+                       static_cast<uint8_t*>(records), pages, max_blocks, blk};
+    llattn::qkv_prepare_kernel<<<dim3((T + llattn::BLK - 1) / llattn::BLK, 8), llattn::PREP_THREADS, 0, as_stream(stream)>>>(a);
+    CU(cudaGetLastError());
+    return LLATTN_OK;
+}
+}  // namespace
+
 int llattn_qk_norm_rope(const float* qkv, const int32_t* pos, const float* gq, const float* gk, float eps,
                         const float* inv_freq, void* q, void* k, void* v, int T, void* stream) {
     if (!qkv || !pos || !gq || !gk || !inv_freq || !q || !k || !v) return fail(LLATTN_EINVAL, "qk_norm_rope: null pointer");
     if (T < 0 || T > 1 << 24) return fail(LLATTN_EINVAL, "qk_norm_rope: T = %d", T);
+    if (!aligned16(k) || !aligned16(v)) return fail(LLATTN_EINVAL, "qk_norm_rope: k and v must be 16-byte aligned");
     if (T == 0) return LLATTN_OK;
-    llattn::qk_norm_rope_kernel<<<dim3(T, 3), llattn::ROPE_THREADS, 0, as_stream(stream)>>>(
-        qkv, pos, gq, gk, eps, inv_freq, static_cast<half*>(q), static_cast<half*>(k), static_cast<half*>(v));
-    CU(cudaGetLastError());
-    return LLATTN_OK;
+    return launch_prepare(qkv, pos, gq, gk, eps, inv_freq, q, k, v, T, nullptr, nullptr, 0, 0, stream);
+}
+
+int llattn_qkv_prepare_commit(const float* qkv, const int32_t* pos, const float* gq, const float* gk, float eps,
+                              const float* inv_freq, void* q, void* k, void* v, int nb, void* cache, const int32_t* pages,
+                              int max_blocks, int blk, void* stream) {
+    if (!qkv || !pos || !gq || !gk || !inv_freq || !q || !k || !v || !cache) return fail(LLATTN_EINVAL, "qkv_prepare_commit: null pointer");
+    if (nb < 0 || nb > 65535) return fail(LLATTN_EINVAL, "qkv_prepare_commit: nb must be in [0, 65535]");
+    if (!pages && (blk < 0 || max_blocks <= 0 || blk + nb > max_blocks))
+        return fail(LLATTN_EINVAL, "qkv_prepare_commit: blocks [%d, %d) outside a cache of %d blocks", blk, blk + nb, max_blocks);
+    if (!aligned16(k) || !aligned16(v) || !aligned16(cache)) return fail(LLATTN_EINVAL, "qkv_prepare_commit: k, v and cache must be 16-byte aligned");
+    if (nb == 0) return LLATTN_OK;
+    return launch_prepare(qkv, pos, gq, gk, eps, inv_freq, q, k, v, nb * llattn::BLK, cache, pages, max_blocks, blk, stream);
 }
 
 // ------------------------------------------------------------------------------------------------------ consumer
@@ -274,6 +295,42 @@ extern "C" int llattn_attention_static(const void* Q, const void* Kf, const void
     CU(cudaGetLastError());
     MergeOut o{static_cast<half*>(O16), O32, LSE, q8, s8, sum8};
     combine_ref_kernel<<<dim3(NKV, nb), MERGE_THREADS, 0, as_stream(stream)>>>(Opart, Mpart, Lpart, nchunks, nblocks, bpc, o);
+    CU(cudaGetLastError());
+    return LLATTN_OK;
+}
+
+// ====================================================================================================== wait self-test
+// What a kernel of this library does when a wait can never complete, shown without making any real kernel fail: four
+// warps wait on barriers nobody will ever arrive on. Warp 0 has `limit_ns` (a millisecond in the test); when its wait
+// runs out it raises the CTA's abort flag, as every role of the attention kernel does, and the other warps - whose own
+// limit is the kernels' two seconds - see the flag at their next poll and leave too. Every warp reports through the
+// error word, the kernel returns normally and the context stays usable.
+namespace llattn {
+__global__ void __launch_bounds__(128) wait_selftest_kernel(unsigned long long limit_ns, int* err, unsigned long long* waited_ns) {
+    __shared__ uint64_t bars[4];
+    __shared__ int abort_flag;
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    if (threadIdx.x == 0) {
+        for (int i = 0; i < 4; ++i) ptx::mbar_init(ptx::smem_u32(&bars[i]), 1);
+        ptx::fence_mbar_init();
+        abort_flag = 0;
+    }
+    __syncthreads();
+    const unsigned long long t0 = ptx::globaltimer_ns();
+    const bool ok = ptx::mbar_wait_limit(ptx::smem_u32(&bars[warp]), 0, &abort_flag, warp == 0 ? limit_ns : ptx::WAIT_LIMIT_NS);
+    const unsigned long long t1 = ptx::globaltimer_ns();
+    if (!ok && lane == 0) {
+        atomicOr(err, warp == 0 ? ERR_WAIT_PRODUCER : warp == 1 ? ERR_WAIT_DEQUANT : warp == 2 ? ERR_WAIT_MMA : ERR_WAIT_SOFTMAX);
+        waited_ns[warp] = t1 - t0;
+    }
+    __syncthreads();
+}
+}  // namespace llattn
+
+extern "C" int llattn_wait_selftest(unsigned long long limit_ns, int* err_word, unsigned long long* waited_ns4, void* stream) {
+    if (!err_word || !waited_ns4) return fail(LLATTN_EINVAL, "wait_selftest: null pointer");
+    if (limit_ns == 0 || limit_ns > 100000000ull) return fail(LLATTN_EINVAL, "wait_selftest: limit of %llu ns; 1 ns .. 100 ms", limit_ns);
+    llattn::wait_selftest_kernel<<<1, 128, 0, as_stream(stream)>>>(limit_ns, err_word, waited_ns4);
     CU(cudaGetLastError());
     return LLATTN_OK;
 }

@@ -53,21 +53,9 @@ __device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity) {
 // every other role that is waiting. Returns false on time-out or abort. A phase that is already complete costs one
 // non-blocking test; otherwise the hardware suspends the thread inside try_wait until the phase completes (the loop
 // body runs about once per wait), and the clock is read every 64 rounds.
-#ifndef LLATTN_WAIT_TRY
-#define LLATTN_WAIT_TRY 0
-#endif
-__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile int* abort_flag) {
-#if LLATTN_WAIT_TRY
-    {
-        uint32_t ok1;
-        asm volatile(
-            "{\n\t.reg .pred p;\n\tmbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\tselp.b32 %0, 1, 0, p;\n\t}\n"
-            : "=r"(ok1) : "r"(bar), "r"(parity) : "memory");
-        if (ok1) return true;
-    }
-#else
+// `limit_ns` is the kernels' WAIT_LIMIT_NS everywhere except in the wait self-test, which passes a millisecond.
+__device__ __forceinline__ bool mbar_wait_limit(uint32_t bar, uint32_t parity, volatile int* abort_flag, unsigned long long limit_ns) {
     if (mbar_try_wait(bar, parity)) return true;
-#endif
     uint32_t ok;
     unsigned long long t0 = 0;
     for (uint32_t it = 0;; ++it) {
@@ -75,13 +63,16 @@ __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatil
             "{\n\t.reg .pred p;\n\tmbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2, %3;\n\tselp.b32 %0, 1, 0, p;\n\t}\n"
             : "=r"(ok) : "r"(bar), "r"(parity), "r"(SUSPEND_HINT_NS) : "memory");
         if (ok) return true;
-        if ((it & 63u) == 63u) {
+        if ((it & 63u) == 63u || limit_ns < WAIT_LIMIT_NS) {
             if (*abort_flag) return false;
             const unsigned long long t = globaltimer_ns();
             if (t0 == 0) t0 = t;
-            else if (t - t0 > WAIT_LIMIT_NS) { *abort_flag = 1; return false; }
+            else if (t - t0 > limit_ns) { *abort_flag = 1; return false; }
         }
     }
+}
+__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile int* abort_flag) {
+    return mbar_wait_limit(bar, parity, abort_flag, WAIT_LIMIT_NS);
 }
 
 // Generic-proxy writes to shared memory (st.shared by threads) must be made visible to the async proxy (the

@@ -103,7 +103,7 @@ def test_captured_step_survives_committed_blocks(api, ctx, orc, pkg):
 
 
 def test_fused_merge_is_deterministic_and_leaves_its_counters_clear(api, ctx, orc, pkg):
-    """Tiles cut into many runs (a 200-block context over 148 CTAs: about 37 runs per kv head): whichever CTA finishes
+    """Tiles cut into many runs (a 200-block context cut into runs of 16 blocks: more than 10 per kv head): whichever CTA finishes
     last folds the tile, always in slot order, so repeated launches agree bit for bit; every output format comes from
     the same fp32 values; and the arrival counters are back at zero, or the second launch would never write."""
     n = 200
@@ -114,7 +114,7 @@ def test_fused_merge_is_deterministic_and_leaves_its_counters_clear(api, ctx, or
     orc.kv_commit(Kc, Vc, cache, n + 1, 0)
     dC, dQ, dK, dV = dev(cache), dev(Q), dev(Kf), dev(Vf)
     plan = ctx.plan([api.Seq(cache=dC, nblocks=n)])
-    assert plan.stats.nitems >= 100
+    assert plan.stats.nitems >= 40
     outs = []
     for rep in range(4):
         O = torch.full((32, 16, 128), float("nan"), dtype=torch.float32, device="cuda")

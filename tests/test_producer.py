@@ -85,3 +85,56 @@ def test_producer_kernel(orc, pkg, T, ctx_tokens):
         pair = np.abs(w32[..., 0:32]) + np.abs(w32[..., 32:64])                 # magnitude of a rotated pair
         bound = np.concatenate([pair, pair, np.zeros_like(pair), np.zeros_like(pair)], -1) * 2.0 ** -7 + 2 * ulp
         assert (diff <= bound).all()
+
+
+@pytest.mark.gpu
+@pytest.mark.parametrize("nb,paged", [(1, False), (16, False), (5, True)])
+def test_producer_fused_with_commit(orc, pkg, nb, paged):
+    """A prefill pass's blocks from fp32 qkv to fp16 Q/K/V AND to their 4736-byte records in one kernel
+    (engine/engine.cu:589-591 runs ops::qk_norm_rope, then attn::kv_commit on its output): Q/K/V are bit-identical to the
+    separate producer, the records byte-equal to committing that output afterwards - with this library's commit kernel,
+    with the oracle packer and, when it travelled, with the reference's own two kernels."""
+    torch = pytest.importorskip("torch")
+    import refkernel
+    api = importlib.import_module(pkg.__name__ + ".api")
+    api.lib()
+    T = 32 * nb
+    qkv, pos, gq, gk, eps = inputs(T, 100 + nb, 32768)
+    f = api.inv_freq()
+    d = lambda a: torch.from_numpy(np.ascontiguousarray(a)).cuda()
+    args = (d(qkv), d(pos), d(gq), d(gk), float(eps), d(f))
+    mk = lambda: (torch.zeros((T, 16, 128), dtype=torch.float16, device="cuda"), torch.zeros((T, 4, 128), dtype=torch.float16, device="cuda"),
+                  torch.zeros((T, 4, 128), dtype=torch.float16, device="cuda"))
+    q0, k0, v0 = mk()
+    api.qk_norm_rope(*args, q0, k0, v0)
+    q1, k1, v1 = mk()
+    maxb, blk = nb + 7, 3
+    if paged:
+        npages = 4 * nb + 11
+        pages = torch.from_numpy(np.random.default_rng(nb).permutation(npages)[:4 * nb].astype(np.int32).reshape(nb, 4)).cuda()
+        want = torch.full((npages, 4736), 0x5A, dtype=torch.uint8, device="cuda")
+        got = want.clone()
+        api.kv_commit_paged(k0.view(nb, 32, 4, 128), v0.view(nb, 32, 4, 128), want, pages)
+        api.qkv_prepare_commit(*args, q1, k1, v1, got, pages=pages)
+    else:
+        want = torch.full((4, maxb, 4736), 0x5A, dtype=torch.uint8, device="cuda")
+        got = want.clone()
+        api.kv_commit(k0.view(nb, 32, 4, 128), v0.view(nb, 32, 4, 128), want, maxb, blk)
+        api.qkv_prepare_commit(*args, q1, k1, v1, got, max_blocks=maxb, blk=blk)
+    torch.cuda.synchronize()
+    for a, b in ((q0, q1), (k0, k1), (v0, v1)):
+        assert torch.equal(a.view(torch.int16), b.view(torch.int16))
+    assert torch.equal(got, want)
+    if not paged:
+        rec = np.full((4, maxb, orc.REC_BYTES), 0x5A, np.uint8)
+        orc.kv_commit(k0.cpu().numpy().reshape(nb, 32, 4, 128), v0.cpu().numpy().reshape(nb, 32, 4, 128), rec, maxb, blk)
+        assert np.array_equal(got.cpu().numpy(), rec)
+        if refkernel.ops_available() and refkernel.available():
+            rq, rk, rv = mk()
+            refkernel.qk_norm_rope(*args, rq, rk, rv)
+            ref = torch.full((4, maxb, 4736), 0x5A, dtype=torch.uint8, device="cuda")
+            refkernel.kv_commit(rk.view(nb, 32, 4, 128), rv.view(nb, 32, 4, 128), ref, maxb, blk)
+            torch.cuda.synchronize()
+            assert torch.equal(ref, got)
+    with pytest.raises(ValueError):
+        api.qkv_prepare_commit(args[0][:33], *args[1:], q1, k1, v1, got, max_blocks=maxb, blk=blk)
