@@ -27,7 +27,7 @@ extras   (N=1 only unless noted): `strong` = 64 sequences IN TOTAL over the N ra
 cpu_baseline / --impl reference = the reference's CPU flow for this path (fp32 simulated quantisation + SDPA,
            torch CPU, all host threads this process may use) on a bounded sample: one sequence x one layer per step,
            scaled to the metric.
---config prefill / ragged print their own JSON line (BASELINE configs 4 and 5): a 16-block prefill pass on 31,744
+--config prefill / ragged print their own JSON line (the prefill and the ragged serving workloads): a 16-block prefill pass on 31,744
            committed tokens followed by the commit of the 16 blocks; 256 ragged sequences balanced over the ranks by
            KV bytes.
 """

@@ -1,8 +1,8 @@
 /*
  * The reference engine's library boundary, kept verbatim: the three functions engine/libllada.cu:13-52 exports and
  * server/server.py:62-71 binds over ctypes. A drop-in libllada.so is the reference's own libllada.cu built with
- * attn_shim.cuh in place of attn.cu; this repository does not re-implement the model forward pass
- * behind these calls.
+ * attn_shim.cuh in place of attn.cu (oracle/Makefile's `dropin` target does exactly that); this repository does not
+ * re-implement the model forward pass behind these calls.
  */
 #ifndef LIBLLADA_H
 #define LIBLLADA_H

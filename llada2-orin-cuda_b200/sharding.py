@@ -16,12 +16,12 @@ def units(nblocks: int, nq: int = 1) -> int:
 
 
 def shard_round_robin(nseq: int, world: int) -> List[List[int]]:
-    """Equal-length batches (BASELINE config 3): sequence i goes to rank i % world."""
+    """Equal-length batches: sequence i goes to rank i % world."""
     return [list(range(r, nseq, world)) for r in range(world)]
 
 
 def shard_lpt(lengths: Sequence[int], world: int, nq: Sequence[int] | None = None) -> List[List[int]]:
-    """Ragged batches (BASELINE config 5): longest-processing-time greedy on KV units. Deterministic: ties go to the
+    """Ragged batches: longest-processing-time greedy on KV units. Deterministic: ties go to the
     lower sequence index, then to the lower rank. Returns, per rank, the sequence indices it serves (ascending)."""
     n = len(lengths)
     nq = [1] * n if nq is None else list(nq)

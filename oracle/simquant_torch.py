@@ -1,4 +1,4 @@
-"""The reference's CPU flow for this path, restated with the same torch operators it uses. TEST / BASELINE
+"""The reference's CPU flow for this path, restated with the same torch operators it uses. TEST / CPU-BASELINE
 INFRASTRUCTURE ONLY (bench.py's CPU-baseline and reference arms time it; nothing that ships calls it).
 
 Follows quant/s06_arbitrate.py:78-89 (fake_quant: per-group asymmetric 4-bit with fp16 scale and min, returned as

@@ -4,8 +4,11 @@ Contexts of 8 K .. 32 K tokens are checked three ways: against the reference's o
 oracle/_ref travelled), against the CPU oracle (fp64 attention over engine-style dequantised records), and through
 properties that do not depend on size: the result must not depend on how the planner cuts the context into runs, and
 the commit -> attend round trip of a prefill pass must equal attending the same records committed beforehand.
-Tolerances as in test_gpu_parity.py for long contexts (rel-L2 <= 2.5e-4, max-abs <= 5e-3 x RMS up to 8 K tokens; at
-32 K the max-abs bound is 1e-2 x RMS: the dominated-row effect described there grows with sqrt(context))."""
+Tolerances of the default path (fp16 P) as in test_gpu_parity.py for long contexts: rel-L2 <= 2.5e-4, max-abs <= 5e-3 x
+RMS for a decode step at 8 K and 32 K tokens (measured 1.7e-3 .. 4.1e-3 depending on where the planner cuts), <= 1e-2
+for the 16-block prefill pass (measured 5.0e-3). The stated bar of 2e-3 x RMS is met at these sizes by the precise path
+(tests/test_gpu_precise.py); tests/test_p_rounding_floor.py shows on the CPU that the default path's residual is the
+fp16 rounding of P."""
 import importlib
 
 import numpy as np
@@ -81,7 +84,7 @@ def test_decode_step_at_8k_and_32k(api, ctx, orc, pkg, nblocks):
     hQ, hK, hV, hC = (x.cpu().numpy() for x in (Q, Kf, Vf, cache))
     O1, L1 = orc.attention(hQ, hK, hV, hC, maxb, nblocks, dq_mode=1)
     assert rel_l2(O, O1) <= 2.5e-4
-    assert relmax(O, O1) <= (5e-3 if nblocks <= 256 else 1e-2)
+    assert relmax(O, O1) <= 5e-3
     assert np.abs(LSE - L1).max() <= 1e-3
     # size-independent property: the answer does not depend on where the planner cuts the context
     for nctas in (4, 37):
@@ -94,7 +97,7 @@ def test_decode_step_at_8k_and_32k(api, ctx, orc, pkg, nblocks):
 
 
 def test_prefill_16_blocks_on_31744_tokens(api, ctx, orc, pkg):
-    """BASELINE config 4: 16 query blocks appended to 992 committed blocks, commit first, then block-causal attention
+    """The prefill workload at full size: 16 query blocks appended to 992 committed blocks, commit first, then block-causal attention
     (engine/engine.cu:591-598); the 16 new records are byte-compared with the oracle packer and the reference kernel."""
     ctx0, nq = 992, 16
     Q, Kf, Vf, cache, maxb = device_case(api, pkg, ctx0, nq, seed=4)
@@ -119,7 +122,7 @@ def test_prefill_16_blocks_on_31744_tokens(api, ctx, orc, pkg):
 
 
 def test_ragged_batch_up_to_32k(api, ctx, orc, pkg):
-    """BASELINE config 5 in miniature: 12 sequences with seeded ragged lengths in [128, 32768] tokens in one call."""
+    """The ragged serving batch in miniature: 12 sequences with seeded ragged lengths in [128, 32768] tokens in one call."""
     lens = [int(x) for x in pkg.workload.ragged_lengths(12, seed=11)]
     lens[0], lens[1] = 4, 1024                                # both ends of the range
     cases = [device_case(api, pkg, n, 1, seed=100 + i) for i, n in enumerate(lens)]
