@@ -22,7 +22,10 @@ def _case(wl, orc, nblocks, nq, seq):
     Q, Kf, Vf = wl.query_blocks(nq, seq=seq)
     maxb = nblocks + nq
     cache = np.zeros((4, maxb, orc.REC_BYTES), np.uint8)
-    orc.kv_commit(Kc, Vc, cache, maxb, 0)
+    if nblocks:
+        orc.kv_commit(Kc, Vc, cache, maxb, 0)
+    if nblocks == 0:
+        cache[:] = 0
     if nq > 1:
         orc.kv_commit(Kf, Vf, cache, maxb, nblocks)
     return Q, Kf, Vf, cache, maxb
@@ -34,7 +37,8 @@ def test_static_entry_point_matches_planned_path_twice(pkg, orc):
     dev = lambda a: torch.from_numpy(np.ascontiguousarray(a)).cuda()
     ctx = api.Context(0)
     err = torch.zeros(1, dtype=torch.int32, device="cuda")
-    for nblocks, nq, seq in [(150, 1, 301), (37, 3, 302)]:
+    # the last two: 16 query blocks (the slot cap decides the split: 2 runs per tile) and an empty context
+    for nblocks, nq, seq in [(150, 1, 301), (37, 3, 302), (40, 16, 303), (0, 1, 304)]:
         Q, Kf, Vf, cache, maxb = _case(pkg.workload, orc, nblocks, nq, seq)
         dQ, dK, dV, dC = dev(Q), dev(Kf), dev(Vf), dev(cache)
         rows = nq * 32
