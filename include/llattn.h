@@ -177,7 +177,9 @@ int llattn_create(int device, llattn_ctx** out);
 void llattn_destroy(llattn_ctx* ctx);
 
 /* Builds the work list for `nseq` sequences (host array) and uploads it; allocates, so not for use inside stream
- * capture. `nctas` <= 0 means one CTA per SM. Every launch of the plan has exactly that many CTAs. */
+ * capture. `nctas` <= 0 means one CTA per SM. Every launch of the plan has exactly that many CTAs. A plan that needs
+ * more scratch than any earlier plan of the context makes the context reallocate its scratch: CUDA graphs captured with
+ * earlier plans then hold stale addresses and must be captured again (create the largest plan first to avoid that). */
 int llattn_plan_create(llattn_ctx* ctx, const llattn_seq* seqs_host, int nseq, int nctas, llattn_plan** out);
 void llattn_plan_destroy(llattn_plan* plan);
 int llattn_plan_get_stats(const llattn_plan* plan, llattn_plan_stats* out);
