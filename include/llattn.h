@@ -83,7 +83,7 @@ int llattn_qkv_prepare_commit(const float* qkv, const int32_t* pos, const float*
                               const float* inv_freq, void* q, void* k, void* v, int nb, void* cache, const int32_t* pages,
                               int max_blocks, int blk, void* stream);
 
-/* ---- consumer of the attention output: the dense projection on the int8 `Act` the merge kernel writes.
+/* ---- consumer of the attention output: the dense projection on the int8 `Act` the attention epilogue writes.
  * Stands in for Engine::gemm<4, 2>(Ly.dense, items_dense, ..., oA.a, ones, HID, HID, nullptr, h, 1, 2)
  * (engine/engine.cu:434 -> moe8::gemm<4, 4, 2, 2>, engine/moe_i8.cu:295-442) for any number of tokens:
  *   Y[n][r] += sum over the K/128 groups g, ascending, of (s_w[r][g] * s[n][g]) * float(P - z[r][g] * sum[n][g]),
@@ -177,7 +177,10 @@ int llattn_create(int device, llattn_ctx** out);
 void llattn_destroy(llattn_ctx* ctx);
 
 /* Builds the work list for `nseq` sequences (host array) and uploads it; allocates, so not for use inside stream
- * capture. `nctas` <= 0 means one CTA per SM. Every launch of the plan has exactly that many CTAs. A plan that needs
+ * capture. `nctas` <= 0, or more than the device has SMs, means one CTA per SM (the CTAs of a launch wait for one
+ * another's partial results, so all of them must be resident: one fits on an SM). Every launch of the plan has exactly
+ * that many CTAs. With fewer (query block, kv head) tiles than CTAs, each tile is cut into equal runs on CTAs of their
+ * own; otherwise the CTAs get contiguous, near-equal shares of the whole unit sequence. A plan that needs
  * more scratch than any earlier plan of the context makes the context reallocate its scratch: CUDA graphs captured with
  * earlier plans then hold stale addresses and must be captured again (create the largest plan first to avoid that). */
 int llattn_plan_create(llattn_ctx* ctx, const llattn_seq* seqs_host, int nseq, int nctas, llattn_plan** out);
@@ -201,10 +204,11 @@ int llattn_plan_update(llattn_plan* plan, const llattn_seq* seqs_host, int nseq,
 int llattn_plan_preview(const llattn_seq* seqs_host, int nseq, int nctas, llattn_plan_stats* stats, int32_t* items_out,
                         int max_items, int32_t* cta_first_out, int max_ctas);
 
-/* One attention pass over every sequence of the plan: ONE kernel launch, no allocation, no host sync. A (query block,
- * kv head) tile that one CTA handles alone is normalised and written by that CTA; a tile spread over several CTAs is
- * folded together by whichever of them finishes last (it reads the others' partial results from the context's scratch,
- * in a fixed order, so results do not depend on timing). Calls that share a context must not overlap on the GPU. */
+/* One attention pass over every sequence of the plan: ONE kernel launch (a cooperative one), no allocation, no host
+ * sync. A (query block, kv head) tile that one CTA handles alone is normalised and written by that CTA; a tile spread
+ * over n CTAs is folded together by those n CTAs once each has finished all of its own runs: each waits (bounded) for
+ * the tile's other partial results in the context's scratch and finishes every n-th row, adding the partial results in
+ * a fixed order, so results do not depend on timing. Calls that share a context must not overlap on the GPU. */
 int llattn_attention(llattn_ctx* ctx, const llattn_plan* plan, const llattn_io* io, void* stream);
 
 /* Same, with Q/Kf/Vf and the requested outputs in HOST memory (pinned, so the copies are asynchronous). The KV cache

@@ -21,8 +21,13 @@
 //                   rescales lazily in the same way); that rare path rescales O in tensor memory, out of line
 // A run that is a tile's only one normalises and writes the outputs in its epilogue. Otherwise its un-normalised O (fp32),
 // reference maximum (log2 units) and row sum go to a partial slot in the format of the reference's Opart/Mpart/Lpart
-// (engine/attn.cu:291-305), and the run that arrives last at the tile folds the slots together (merge_kernel.cuh has the
-// row routines); with the reference-shaped operator pair the caller's attn_combine launch does that instead.
+// (engine/attn.cu:291-305) and it counts itself in at the tile's arrival counter. When a CTA has no runs left it returns
+// to its split tiles: it waits (bounded) until every run of the tile is counted, then folds its share of the tile's
+// rows (run k of n takes rows k, k + n, ...; all sixteen warps, a warp per row; merge_kernel.cuh) and writes their
+// outputs, so a tile cut into n runs is folded by n SMs at once. A CTA only ever waits after all of its own runs are
+// out, so the waits cannot form a cycle; they need every CTA of the launch to be on an SM, which a grid of at most one
+// CTA per SM launched cooperatively guarantees. With the reference-shaped operator pair the caller's attn_combine
+// launch folds instead.
 //
 // Operands. Q (the A operand of S = Q K^T) lives in tensor memory for the whole item: row i in lane i, 64 columns of
 // fp16 pairs. K and V tiles live in shared memory in the 128-byte-swizzle layout: a tile is made of blocks of
@@ -131,9 +136,10 @@ struct KParams {
     float* Lpart;
     float sl2;                     // softmax scale * log2(e)
     int* err;
-    // list mode with fused merge (merge != nullptr): the run that completes an output tile writes the tile's outputs
+    // list mode with folding in the kernel (merge != nullptr)
     const MergeDesc* merge;        // per output tile (WorkItem::tile indexes it)
-    int* tile_counters;            // [tiles][4]: runs of the tile whose rows of lane quarter w are out; back at 0 after the launch
+    int* tile_counters;            // [tiles][4]: [0] softmax warps whose rows of a run are out (4 per run), [1] warps that
+                                   // have folded their share (16 per run); both back at 0 when the launch ends
     MergeOut out;
     size_t cache_offset;           // bytes added to every sequence's cache pointer: the layer this launch reads
     // reference-grid mode (items == nullptr): CTA i is (kvh = i % 4, chunk = (i / 4) % ref_nchunks, jb = i / (4 * ref_nchunks))
@@ -578,9 +584,9 @@ __device__ __forceinline__ void attn_tile_body(const KParams& p, const int cta) 
             }
             if (!alive) break;
             // ---- epilogue. A run that is its tile's only one writes the outputs straight from tensor memory. Otherwise
-            // it stores its un-normalised O, reference exponent and row sum as a partial result; the run whose rows
-            // complete the tile (arrival counter per tile and lane quarter) folds the tile's partials together, in slot
-            // order whoever comes last, and writes the outputs. It never waits for another CTA.
+            // it stores its un-normalised O, reference exponent and row sum as a partial result and counts itself in at
+            // the tile's arrival counter; the tile's runs fold it together once the CTAs have no runs left (end of this
+            // function).
             const uint32_t tl = t - 1;
             if (!ptx::mbar_wait(BAR(B_PV_DONE + (tl & 1)), (tl >> 1) & 1, abort_flag)) { alive = false; errbits |= ERR_WAIT_SOFTMAX; break; }
             ptx::tc_fence_after();
@@ -615,33 +621,10 @@ __device__ __forceinline__ void attn_tile_body(const KParams& p, const int cta) 
                 }
                 p.Lpart[size_t(w.slot) * QR + row] = lsum;
                 p.Mpart[size_t(w.slot) * QR + row] = mref;
-                if (fused) {
+                if (fused) {                   // this warp's 32 rows of the run are out: count it in
                     __threadfence();
                     __syncwarp();
-                    int before = 0;
-                    if (lane == 0) before = atomicAdd(p.tile_counters + 4 * w.tile + warp, 1);
-                    before = __shfl_sync(0xffffffffu, before, 0);
-                    if (before == md.nslots - 1) {
-                        if (lane == 0) p.tile_counters[4 * w.tile + warp] = 0;
-                        __threadfence();
-                        row_scale(p.Mpart, p.Lpart, md.slot_begin, md.nslots, row, M, den);
-#pragma unroll 1
-                        for (int c = 0; c < 4; ++c) {      // the merged row goes back into this CTA's (finished) accumulator
-                            float acc[32];
-                            uint32_t r[32];
-                            row_gather(p.Opart, p.Mpart, md.slot_begin, md.nslots, row, M, c, acc);
-#pragma unroll
-                            for (int g = 0; g < 4; ++g)
-#pragma unroll
-                                for (int k = 0; k < 4; ++k) {
-                                    r[8 * g + 2 * k] = __float_as_uint(acc[8 * g + k]);
-                                    r[8 * g + 2 * k + 1] = __float_as_uint(acc[8 * g + 4 + k]);
-                                }
-                            ptx::tmem_st32(tlane + TM_O + 32 * c, r);
-                        }
-                        ptx::tmem_wait_st();
-                        finish = true;
-                    }
+                    if (lane == 0) atomicAdd(p.tile_counters + 4 * w.tile, 1);
                 }
             }
             if (finish) {
@@ -979,6 +962,46 @@ __device__ __forceinline__ void attn_tile_body(const KParams& p, const int cta) 
             if (!ptx::mbar_wait(BAR(B_SPARE + 1), 0, &never)) errbits |= ERR_WAIT_TEARDOWN;
         }
 #endif
+    }
+
+    // ---- split tiles. Every run of this CTA is stored and counted by now, so nothing this CTA waits for depends on
+    // this CTA: for each of its runs that is part of a split tile, wait (bounded) until all of the tile's runs are
+    // counted in, then all sixteen warps finish this run's share of the rows, a warp per row. The last warp to leave a
+    // tile puts both of its counters back to zero for the next launch.
+    if (p.merge != nullptr) {
+#pragma unroll 1
+        for (int ii = i0_any; ii < i1_any; ++ii) {
+            WorkItem w; SeqDesc sq;
+            if (!fetch_item(p, ii, w, sq)) continue;
+            const MergeDesc md = p.merge[w.tile];
+            if (md.nslots <= 1) continue;
+            int* counters = p.tile_counters + 4 * w.tile;
+            if (!wait_count(counters, SOFTMAX_WARPS * md.nslots, abort_flag, ptx::WAIT_LIMIT_NS)) {
+                errbits |= ERR_WAIT_FOLD;
+                *abort_flag = 1;
+                break;
+            }
+            constexpr int NW = ATTN_THREADS / 32;
+            const int r0 = (w.slot - md.slot_begin) + md.nslots * warp, step = md.nslots * NW;
+            if (md.nslots == 2) {
+#pragma unroll 1
+                for (int r = r0; r < QR; r += 4 * step) {
+                    const int rows[4] = {r, r + step < QR ? r + step : -1, r + 2 * step < QR ? r + 2 * step : -1, r + 3 * step < QR ? r + 3 * step : -1};
+                    fold_rows_few<4, 2>(p.Opart, p.Mpart, p.Lpart, md, rows, lane, p.out);
+                }
+            } else if (md.nslots <= 4) {
+#pragma unroll 1
+                for (int r = r0; r < QR; r += 2 * step) {
+                    const int rows[2] = {r, r + step < QR ? r + step : -1};
+                    fold_rows_few<2, 4>(p.Opart, p.Mpart, p.Lpart, md, rows, lane, p.out);
+                }
+            } else {
+#pragma unroll 1
+                for (int r = r0; r < QR; r += step) fold_row_warp(p.Opart, p.Mpart, p.Lpart, md, r, lane, p.out);
+            }
+            __syncwarp();
+            if (lane == 0 && atomicAdd(counters + 1, 1) == (ATTN_THREADS / 32) * md.nslots - 1) { counters[0] = 0; counters[1] = 0; }
+        }
     }
 
     if (errbits && p.err) atomicOr(p.err, errbits);

@@ -48,7 +48,7 @@ struct MergeDesc {
 // Device error word bits (set by a kernel whose bounded wait ran out, or whose shared-memory base is not aligned).
 enum : int {
     ERR_WAIT_PRODUCER = 1, ERR_WAIT_DEQUANT = 2, ERR_WAIT_MMA = 4, ERR_WAIT_SOFTMAX = 8, ERR_WAIT_TEARDOWN = 16,
-    ERR_BAD_ITEM = 32, ERR_SMEM_ALIGN = 64
+    ERR_BAD_ITEM = 32, ERR_SMEM_ALIGN = 64, ERR_WAIT_FOLD = 128
 };
 
 }  // namespace llattn

@@ -6,6 +6,8 @@
 #include <cstdarg>
 #include <cstdio>
 #include <cstring>
+#include <cstdlib>
+#include <cmath>
 #include <mutex>
 #include <new>
 #include <vector>

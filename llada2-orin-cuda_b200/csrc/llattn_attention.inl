@@ -21,35 +21,43 @@ int grow_workspace(llattn_ctx* c, size_t need) {
 // one fresh block, in that order) into `nctas` contiguous shares of near-equal size. A share boundary inside a tile
 // falls on a multiple of 4 units from the tile's start so that 128-key MMA tiles stay full, and a run is never
 // shorter than `min_units` unless the tile itself is. Every run gets its own partial slot; the slots of one tile are
-// consecutive.
+// consecutive. When there are no more output tiles than CTAs the tiles are cut one by one instead (see build_plan).
 struct HostPlan {
     std::vector<llattn::SeqDesc> seqs;
     std::vector<llattn::WorkItem> items;
     std::vector<int32_t> cta_first;
     std::vector<llattn::MergeDesc> merge;
-    int64_t total_units = 0, max_cta_units = 0;
+    int64_t total_units = 0, max_cta_units = 0, max_cta_cost = 0;
     int nq_total = 0, used_ctas = 0;
 };
 
-int build_plan(const llattn_seq* seqs, int nseq, int nctas, HostPlan& hp) {
-    using namespace llattn;
-    hp.seqs.resize(nseq);
-    int64_t total = 0;
-    int nq_total = 0;
-    for (int s = 0; s < nseq; ++s) {
-        const llattn_seq& q = seqs[s];
-        if (!q.cache && q.nblocks + q.nq - 1 > 0) return fail(LLATTN_EINVAL, "plan: sequence %d has a null cache", s);
-        if (q.nblocks < 0 || q.nq < 1 || q.q_first < 0 || q.head_stride < 0)
-            return fail(LLATTN_EINVAL, "plan: sequence %d has a negative count (nblocks %d, nq %d, q_first %d)", s, q.nblocks, q.nq, q.q_first);
-        if (q.nblocks + q.nq - 1 > q.head_stride)
-            return fail(LLATTN_EINVAL, "plan: sequence %d reads %d blocks but head_stride is %d", s, q.nblocks + q.nq - 1, q.head_stride);
-        if (q.cache && !aligned16(q.cache)) return fail(LLATTN_EINVAL, "plan: sequence %d cache is not 16-byte aligned", s);
-        hp.seqs[s] = SeqDesc{static_cast<const uint8_t*>(q.cache), q.pages, q.head_stride, q.nblocks, q.nq, q.q_first};
-        for (int j = 0; j < q.nq; ++j) total += int64_t(NKV) * (q.nblocks + j + 1);
-        nq_total = std::max(nq_total, q.q_first + q.nq);
+// What a CTA's list costs, in the time of a unit (about a third of a microsecond): its units, a start-up charge per run
+// (query load, first records, the pipeline filling up, the epilogue), and for a run of a split tile the partial result's
+// round trip through the L2 and its share of the folding.
+constexpr int64_t RUN_STARTUP_UNITS = 20, RUN_SPLIT_UNITS = 6;
+// A piece of a tile shorter than this is not worth a run of its own: the cut moves to the tile's end (or start) instead.
+constexpr int SHORTEST_PIECE = 12;
+
+void finish_plan(HostPlan& hp, int nctas) {
+    if (hp.cta_first.back() != int32_t(hp.items.size())) hp.cta_first.push_back(int32_t(hp.items.size()));
+    hp.used_ctas = int(hp.cta_first.size()) - 1;
+    // the launch always has `nctas` CTAs (a captured graph keeps its grid when the plan is updated): the rest get no items
+    while (int(hp.cta_first.size()) < nctas + 1) hp.cta_first.push_back(int32_t(hp.items.size()));
+    hp.max_cta_units = hp.max_cta_cost = 0;
+    for (size_t c = 0; c + 1 < hp.cta_first.size(); ++c) {
+        int64_t u = 0;
+        for (int i = hp.cta_first[c]; i < hp.cta_first[c + 1]; ++i) u += hp.items[i].rec_count + hp.items[i].fresh;
+        hp.max_cta_units = std::max(hp.max_cta_units, u);
+        int64_t cost = u;
+        for (int i = hp.cta_first[c]; i < hp.cta_first[c + 1]; ++i)
+            cost += RUN_STARTUP_UNITS + (hp.merge[hp.items[i].tile].nslots > 1 ? RUN_SPLIT_UNITS : 0);
+        hp.max_cta_cost = std::max(hp.max_cta_cost, cost);
     }
-    hp.total_units = total;
-    hp.nq_total = nq_total;
+}
+
+// Contiguous shares of the flattened unit sequence (see above).
+void cut_contiguous(const llattn_seq* seqs, int nseq, int nctas, int64_t total, HostPlan& hp) {
+    using namespace llattn;
     constexpr int64_t MIN_UNITS = 16;
     // The share of the CTA being filled is re-derived from what is left (units and CTAs), so rounding a cut down to a
     // tile boundary never pushes work into an extra CTA: the plan uses at most `nctas` CTAs.
@@ -77,7 +85,11 @@ int build_plan(const llattn_seq* seqs, int nseq, int nctas, HostPlan& hp) {
                 const int slot0 = slot, tile = int(hp.merge.size());
                 while (done < U) {
                     int take = int(std::min<int64_t>(room, U - done));
-                    if (take < U - done) take = take / TILE_UNITS * TILE_UNITS;     // keep the cut on a tile boundary
+                    if (take < U - done) {
+                        take = take / TILE_UNITS * TILE_UNITS;                      // keep the cut on a tile boundary
+                        if (U - done - take < SHORTEST_PIECE) take = U - done;      // no short tail for the next CTA
+                        else if (take < SHORTEST_PIECE && int(hp.items.size()) > hp.cta_first.back()) take = 0;   // no short head here
+                    }
                     if (take == 0) { next_cta(); continue; }
                     const int rec_cnt = std::min(take, nrec - done);
                     hp.items.push_back(WorkItem{s, j, h, done, std::max(rec_cnt, 0), done + take == U ? 1 : 0, slot++, tile});
@@ -88,15 +100,77 @@ int build_plan(const llattn_seq* seqs, int nseq, int nctas, HostPlan& hp) {
                 }
                 hp.merge.push_back(MergeDesc{seqs[s].q_first + j, h, slot0, slot - slot0});
             }
-    if (hp.cta_first.back() != int32_t(hp.items.size())) hp.cta_first.push_back(int32_t(hp.items.size()));
-    hp.used_ctas = int(hp.cta_first.size()) - 1;
-    // the launch always has `nctas` CTAs (a captured graph keeps its grid when the plan is updated): the rest get no items
-    while (int(hp.cta_first.size()) < nctas + 1) hp.cta_first.push_back(int32_t(hp.items.size()));
-    hp.max_cta_units = 0;
-    for (size_t c = 0; c + 1 < hp.cta_first.size(); ++c) {
-        int64_t u = 0;
-        for (int i = hp.cta_first[c]; i < hp.cta_first[c + 1]; ++i) u += hp.items[i].rec_count + hp.items[i].fresh;
-        hp.max_cta_units = std::max(hp.max_cta_units, u);
+    finish_plan(hp, nctas);
+}
+
+// Every run on a CTA of its own: each output tile is cut into equal runs, their number in proportion to the tile's
+// length (and no run shorter than about sqrt(units of the tile)). Possible when there are no more output tiles than CTAs; better
+// than contiguous shares when the step is a latency problem (a handful of sequences), because no CTA then pays the
+// start-up of two runs one after the other.
+void cut_per_tile(const llattn_seq* seqs, int nseq, int nctas, int64_t total, HostPlan& hp) {
+    using namespace llattn;
+    std::vector<int> runs;
+    int64_t given = 0;
+    for (int s = 0; s < nseq; ++s)
+        for (int j = 0; j < seqs[s].nq; ++j)
+            for (int h = 0; h < NKV; ++h) {
+                const int64_t U = seqs[s].nblocks + j + 1;
+                // a run costs about a unit's time per unit plus one and a quarter units per run of its tile (its partial
+                // result is written, waited for and read back): the sum is smallest near sqrt(U) units per run
+                const int64_t shortest = std::max<int64_t>(TILE_UNITS, int64_t(1.1 * std::sqrt(double(U)) + 0.5));
+                const int64_t by_share = U * nctas / total, by_length = (U + shortest - 1) / shortest;
+                runs.push_back(int(std::max<int64_t>(1, std::min(by_share, by_length))));
+                given += runs.back();
+            }
+    while (given > nctas) {                       // only when many tiles were rounded up to one run
+        auto it = std::max_element(runs.begin(), runs.end());
+        --*it; --given;
+    }
+    hp.cta_first.assign(1, 0);
+    int slot = 0, t = 0;
+    for (int s = 0; s < nseq; ++s)
+        for (int j = 0; j < seqs[s].nq; ++j)
+            for (int h = 0; h < NKV; ++h, ++t) {
+                const int nrec = seqs[s].nblocks + j, U = nrec + 1, slot0 = slot;
+                const int per = std::max(TILE_UNITS, ((U + runs[t] - 1) / runs[t] + TILE_UNITS - 1) / TILE_UNITS * TILE_UNITS);
+                for (int done = 0; done < U; done += per) {
+                    const int take = std::min(per, U - done);
+                    hp.items.push_back(WorkItem{s, j, h, done, std::max(std::min(take, nrec - done), 0), done + take == U ? 1 : 0, slot++, t});
+                    hp.cta_first.push_back(int32_t(hp.items.size()));
+                }
+                hp.merge.push_back(MergeDesc{seqs[s].q_first + j, h, slot0, slot - slot0});
+            }
+    finish_plan(hp, nctas);
+}
+
+int build_plan(const llattn_seq* seqs, int nseq, int nctas, HostPlan& hp) {
+    using namespace llattn;
+    hp.seqs.resize(nseq);
+    int64_t total = 0, ntile_out = 0;
+    int nq_total = 0;
+    for (int s = 0; s < nseq; ++s) {
+        const llattn_seq& q = seqs[s];
+        if (!q.cache && q.nblocks + q.nq - 1 > 0) return fail(LLATTN_EINVAL, "plan: sequence %d has a null cache", s);
+        if (q.nblocks < 0 || q.nq < 1 || q.q_first < 0 || q.head_stride < 0)
+            return fail(LLATTN_EINVAL, "plan: sequence %d has a negative count (nblocks %d, nq %d, q_first %d)", s, q.nblocks, q.nq, q.q_first);
+        if (q.nblocks + q.nq - 1 > q.head_stride)
+            return fail(LLATTN_EINVAL, "plan: sequence %d reads %d blocks but head_stride is %d", s, q.nblocks + q.nq - 1, q.head_stride);
+        if (q.cache && !aligned16(q.cache)) return fail(LLATTN_EINVAL, "plan: sequence %d cache is not 16-byte aligned", s);
+        hp.seqs[s] = SeqDesc{static_cast<const uint8_t*>(q.cache), q.pages, q.head_stride, q.nblocks, q.nq, q.q_first};
+        for (int j = 0; j < q.nq; ++j) total += int64_t(NKV) * (q.nblocks + j + 1);
+        ntile_out += int64_t(NKV) * q.nq;
+        nq_total = std::max(nq_total, q.q_first + q.nq);
+    }
+    hp.total_units = total;
+    hp.nq_total = nq_total;
+    cut_contiguous(seqs, nseq, nctas, total, hp);
+    if (ntile_out <= nctas) {
+        HostPlan alt;
+        cut_per_tile(seqs, nseq, nctas, total, alt);
+        if (alt.max_cta_cost < hp.max_cta_cost) {
+            hp.items.swap(alt.items); hp.cta_first.swap(alt.cta_first); hp.merge.swap(alt.merge);
+            hp.used_ctas = alt.used_ctas; hp.max_cta_units = alt.max_cta_units; hp.max_cta_cost = alt.max_cta_cost;
+        }
     }
     return LLATTN_OK;
 }
@@ -231,7 +305,9 @@ int llattn_plan_create(llattn_ctx* c, const llattn_seq* seqs, int nseq, int ncta
     if (!c || !seqs || !out) return fail(LLATTN_EINVAL, "plan_create: null pointer");
     *out = nullptr;
     if (nseq < 1) return fail(LLATTN_EINVAL, "plan_create: nseq must be positive");
-    if (nctas <= 0) nctas = c->num_sms;
+    // One CTA fits on an SM, and a CTA waits (bounded) for the other runs of the tiles it shares: every CTA of the launch
+    // must be on an SM at the same time, so the grid never exceeds the SM count (the launch is a cooperative one).
+    if (nctas <= 0 || nctas > c->num_sms) nctas = c->num_sms;
     HostPlan hp;
     if (int rc = build_plan(seqs, nseq, nctas, hp)) return rc;
     if (hp.merge.size() > COUNTER_TILES) return fail(LLATTN_EINVAL, "plan_create: %zu output tiles, at most %d per call", hp.merge.size(), COUNTER_TILES);
@@ -364,9 +440,11 @@ int llattn_attention(llattn_ctx* c, const llattn_plan* pl, const llattn_io* io, 
     p.tile_counters = static_cast<int*>(c->workspace);
     p.out = MergeOut{static_cast<half*>(io->O16), io->O32, io->LSE, io->q8, io->s8, io->sum8};
     p.cache_offset = io->cache_offset;
-    if (io->flags & LLATTN_IO_PRECISE_P) attn_tile_kernel<true><<<pl->launch_ctas, ATTN_THREADS, ATTN_SMEM_BYTES, as_stream(stream)>>>(p);
-    else attn_tile_kernel<false><<<pl->launch_ctas, ATTN_THREADS, ATTN_SMEM_BYTES, as_stream(stream)>>>(p);
-    CU(cudaGetLastError());
+    // cooperative: the driver starts the grid only when all of its CTAs can be resident together (see plan_create)
+    void* args[] = {&p};
+    const void* fn = (io->flags & LLATTN_IO_PRECISE_P) ? reinterpret_cast<const void*>(attn_tile_kernel<true>)
+                                                       : reinterpret_cast<const void*>(attn_tile_kernel<false>);
+    CU(cudaLaunchCooperativeKernel(fn, dim3(pl->launch_ctas), dim3(ATTN_THREADS), args, ATTN_SMEM_BYTES, as_stream(stream)));
     return LLATTN_OK;
 }
 

@@ -7,9 +7,10 @@
 //
 // One THREAD owns one query row (all 128 dims): that is how the attention kernel holds its accumulator (one tensor-memory
 // lane per row), so the same code finishes a row whether its values come from tensor memory (the attention kernel's
-// epilogue: a tile made of a single run, or the run that arrives last at a tile) or from the partial slots in global
-// memory (the reference-shaped operator pair, combine_ref_kernel below). A row is handled 32 dims at a time; the slots
-// of a tile are always added in slot order, so the result does not depend on which run finishes last.
+// epilogue for a tile made of a single run) or from the partial slots in global memory (the reference-shaped operator
+// pair, combine_ref_kernel below). A row is handled 32 dims at a time. Tiles the attention kernel itself cut into several
+// runs are folded by the warp-per-row routines further down. The slots of a tile are always added in slot order, so the
+// result does not depend on which run finishes last.
 #pragma once
 #include <cuda_fp16.h>
 #include "common.cuh"
@@ -113,6 +114,150 @@ __device__ __forceinline__ float absmax32(const float (&v)[32]) {
 __device__ __forceinline__ void row_finish(const MergeOut& o, const RowOut& ro, float M, float den) {
     if (o.LSE) o.LSE[ro.row * NQH + ro.head] = 0.6931471805599453f * (M + log2f(den));
     if (o.q8) { o.s8[ro.row * NQH + ro.head] = ro.qscale; o.sum8[ro.row * NQH + ro.head] = ro.qsum; }
+}
+
+// ------------------------------------------------------------------------------------------------------------------
+// Shared folding of a split tile (the attention kernel's own path). Every run of a tile that was cut into several runs
+// stores its partial result and counts itself in; when a CTA has no runs left it comes back to each of its split tiles,
+// waits until all of that tile's runs are counted, and finishes an equal share of the tile's rows: run k of n takes
+// rows k, k + n, k + 2n, ... So a tile cut into n runs is folded by n SMs at once, each reading as much as it wrote.
+// Here a WARP owns a row: lane l holds dims 4l .. 4l+3, a slot's row is one coalesced 512-byte read, and the loads of up
+// to FOLD_BATCH slots are in flight together. The sums run in slot order, like everywhere else.
+constexpr int FOLD_BATCH = 12;
+
+__device__ __forceinline__ int load_acquire(const int* p) {
+    int v;
+    asm volatile("ld.acquire.gpu.global.s32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
+    return v;
+}
+
+// Warp-uniform bounded wait until *counter reaches `target`. False if the CTA gave up elsewhere or the limit ran out.
+__device__ __forceinline__ bool wait_count(const int* counter, int target, volatile int* abort_flag, unsigned long long limit_ns) {
+    unsigned long long t0 = 0;
+    for (unsigned it = 0;; ++it) {
+        if (load_acquire(counter) >= target) return true;
+        if (*abort_flag) return false;
+        if ((it & 15u) == 15u) {
+            unsigned long long t;
+            asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
+            if (t0 == 0) t0 = t;
+            else if (t - t0 > limit_ns) return false;
+        }
+        __nanosleep(100);
+    }
+}
+
+// A folded row (reference exponent M, weighted row sum den, un-normalised dims 4 lane .. 4 lane + 3) to every requested
+// output, by the warp that owns the row.
+__device__ __forceinline__ void emit_row_warp(float M, float den, const float4& acc, const MergeDesc& md, int r, int lane,
+                                              const MergeOut& o) {
+    const float inv = 1.f / den;
+    const float val[4] = {acc.x * inv, acc.y * inv, acc.z * inv, acc.w * inv};
+    const size_t row = size_t(md.q_index) * BLK + (r >> 2);
+    const int head = 4 * md.kvh + (r & 3);
+    const size_t at = (row * NQH + head) * D + 4 * lane;
+    if (o.O32) *reinterpret_cast<float4*>(o.O32 + at) = make_float4(val[0], val[1], val[2], val[3]);
+    if (o.O16) {
+        const half2 a = __floats2half2_rn(val[0], val[1]), b = __floats2half2_rn(val[2], val[3]);
+        *reinterpret_cast<uint2*>(o.O16 + at) = make_uint2(*reinterpret_cast<const uint32_t*>(&a), *reinterpret_cast<const uint32_t*>(&b));
+    }
+    if (o.LSE && lane == 0) o.LSE[row * NQH + head] = 0.6931471805599453f * (M + log2f(den));
+    if (o.q8) {
+        float m = fmaxf(fmaxf(fabsf(val[0]), fabsf(val[1])), fmaxf(fabsf(val[2]), fabsf(val[3])));
+#pragma unroll
+        for (int d = 16; d; d >>= 1) m = fmaxf(m, __shfl_xor_sync(0xffffffffu, m, d));
+        const float qscale = fmaxf(__fdiv_rn(m, 127.f), 1e-30f);
+        int code[4], total = 0;
+#pragma unroll
+        for (int k = 0; k < 4; ++k) { code[k] = max(-127, min(127, __float2int_rn(__fdiv_rn(val[k], qscale)))); total += code[k]; }
+        const uint32_t packed = uint32_t(code[0] & 0xff) | uint32_t(code[1] & 0xff) << 8 | uint32_t(code[2] & 0xff) << 16 | uint32_t(code[3] & 0xff) << 24;
+        *reinterpret_cast<uint32_t*>(o.q8 + row * 2048 + frag_pos(head * D + 4 * lane)) = packed;
+#pragma unroll
+        for (int d = 16; d; d >>= 1) total += __shfl_xor_sync(0xffffffffu, total, d);
+        if (lane == 0) { o.s8[row * NQH + head] = qscale; o.sum8[row * NQH + head] = total; }
+    }
+}
+
+// One row of a split tile, by one warp: fold the slots, normalise, write every requested output.
+constexpr int FOLD_MAX_SLOTS = 160;           // slots of one tile: at most one per CTA of the launch (148 SMs)
+__device__ __forceinline__ void fold_row_warp(const float* Opart, const float* Mpart, const float* Lpart, const MergeDesc& md,
+                                              int r, int lane, const MergeOut& o) {
+    const int n = md.nslots;
+    const size_t i0 = size_t(md.slot_begin) * QR + r;              // the row in the tile's first slot; + QR per slot
+    // reference exponents and row sums of all slots at once: lane l holds slots l, l + 32, ...
+    float mm[FOLD_MAX_SLOTS / 32], ll[FOLD_MAX_SLOTS / 32];
+    float M = -INFINITY;
+#pragma unroll
+    for (int c = 0; c < FOLD_MAX_SLOTS / 32; ++c) {
+        const int s = 32 * c + lane;
+        mm[c] = s < n ? __ldcg(Mpart + i0 + size_t(s) * QR) : -INFINITY;
+        ll[c] = s < n ? __ldcg(Lpart + i0 + size_t(s) * QR) : 0.f;
+        M = fmaxf(M, mm[c]);
+    }
+#pragma unroll
+    for (int d = 16; d; d >>= 1) M = fmaxf(M, __shfl_xor_sync(0xffffffffu, M, d));
+#pragma unroll
+    for (int c = 0; c < FOLD_MAX_SLOTS / 32; ++c) mm[c] = exp2f(mm[c] - M);      // now the slots' weights
+    float den = 0.f;
+    float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
+#pragma unroll
+    for (int c = 0; c < FOLD_MAX_SLOTS / 32; ++c) {
+        if (32 * c >= n) break;
+        const int nc = min(32, n - 32 * c);
+#pragma unroll 1
+        for (int s0 = 0; s0 < nc; s0 += FOLD_BATCH) {
+            float4 v[FOLD_BATCH];
+#pragma unroll
+            for (int k = 0; k < FOLD_BATCH; ++k)       // past the end: the chunk's last slot again, not used below
+                v[k] = __ldcg(reinterpret_cast<const float4*>(Opart + (i0 + size_t(32 * c + min(s0 + k, nc - 1)) * QR) * D) + lane);
+#pragma unroll
+            for (int k = 0; k < FOLD_BATCH; ++k) {
+                const float f = __shfl_sync(0xffffffffu, mm[c], (s0 + k) & 31), l = __shfl_sync(0xffffffffu, ll[c], (s0 + k) & 31);
+                if (s0 + k < nc) {
+                    den += f * l;
+                    acc.x += f * v[k].x; acc.y += f * v[k].y; acc.z += f * v[k].z; acc.w += f * v[k].w;
+                }
+            }
+        }
+    }
+    emit_row_warp(M, den, acc, md, r, lane, o);
+}
+
+// A few rows at once for tiles cut into NS <= 4 runs (what a large batch produces: a tile straddling two CTAs): the
+// loads of R rows x NS slots are all issued before the first sum, so a warp's share of a tile takes one round trip to
+// the L2 instead of one per row. rows[q] < 0: no row.
+template <int R, int NS>
+__device__ __forceinline__ void fold_rows_few(const float* Opart, const float* Mpart, const float* Lpart, const MergeDesc& md,
+                                              const int (&rows)[R], int lane, const MergeOut& o) {
+    const int n = md.nslots;
+    float m[R][NS], l[R][NS];
+    float4 v[R][NS];
+#pragma unroll
+    for (int q = 0; q < R; ++q)
+#pragma unroll
+        for (int s = 0; s < NS; ++s) {
+            const size_t i = (size_t(md.slot_begin) + min(s, n - 1)) * QR + max(rows[q], 0);
+            m[q][s] = __ldcg(Mpart + i);
+            l[q][s] = __ldcg(Lpart + i);
+            v[q][s] = __ldcg(reinterpret_cast<const float4*>(Opart + i * D) + lane);
+        }
+#pragma unroll
+    for (int q = 0; q < R; ++q) {
+        if (rows[q] < 0) continue;
+        float M = m[q][0];
+#pragma unroll
+        for (int s = 1; s < NS; ++s) if (s < n) M = fmaxf(M, m[q][s]);
+        float den = 0.f;
+        float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
+#pragma unroll
+        for (int s = 0; s < NS; ++s)
+            if (s < n) {
+                const float f = exp2f(m[q][s] - M);
+                den += f * l[q][s];
+                acc.x += f * v[q][s].x; acc.y += f * v[q][s].y; acc.z += f * v[q][s].z; acc.w += f * v[q][s].w;
+            }
+        emit_row_warp(M, den, acc, md, rows[q], lane, o);
+    }
 }
 
 // Reference-shaped path: grid (4 kv heads, nb), 128 threads = the tile's rows; slots laid out [jb][kvh][nchunks] as

@@ -10,6 +10,7 @@ import os
 import subprocess
 import sys
 
+import numpy as np
 import pytest
 
 from conftest import PKG_NAME, ROOT
@@ -20,9 +21,12 @@ REF = os.path.join(ROOT, "oracle", "_ref")
 VOCAB, NPROMPT, NEW = 4096, 104, 56
 
 
-def run_engine(lib, directory):
+def run_engine(lib, directory, dump=None):
+    env = dict(os.environ)
+    if dump:
+        env["LLADA_DUMPX"] = dump                        # engine/decode.cu:329-336: the readout's input, every step
     p = subprocess.run([sys.executable, os.path.join(ROOT, "tests", "engine_run.py"), lib, directory, str(NPROMPT),
-                        str(NEW), str(VOCAB)], capture_output=True, text=True, timeout=600)
+                        str(NEW), str(VOCAB)], capture_output=True, text=True, timeout=600, env=env)
     assert p.returncode == 0, f"{os.path.basename(lib)} ended with {p.returncode}:\n{p.stderr[-2000:]}"
     return json.loads(p.stdout.strip().splitlines()[-1])
 
@@ -63,11 +67,47 @@ def test_reference_engine_runs_on_the_new_kernels(directory, capsys):
     check_run(ref)
     a, b = mine["runs"][0]["ids"], ref["runs"][0]["ids"]
     same = sum(x == y for x, y in zip(a, b))
-    prefix = next((i for i, (x, y) in enumerate(zip(a, b)) if x != y), len(a))
     with capsys.disabled():
-        print(f"\n[engine] drop-in vs reference kernels: {same}/{len(a)} generated tokens equal, common prefix {prefix}; "
+        print(f"\n[engine, 3 layers with MoE] drop-in vs reference kernels: {same}/{len(a)} generated tokens equal; "
               f"steps {mine['runs'][0]['steps']:.0f} vs {ref['runs'][0]['steps']:.0f}; "
               f"generate {mine['runs'][0]['seconds']:.3f} s vs {ref['runs'][0]['seconds']:.3f} s")
-    # random weights give nearly flat token distributions, so one flipped near-tie changes everything decoded after it:
-    # the first decoded block's prompt-conditioned tokens agree, whole-sequence equality is reported, not required
-    assert same >= 1
+    # No token-level claim: random routers put many tokens on a top-8 boundary, so a one-code difference in an int8
+    # activation re-routes a token and everything decoded afterwards differs. The numerical comparison is the next test.
+
+
+def hidden_states(path):
+    """LLADA_DUMPX records: per denoising step the final hidden state as int8 codes [32][2048] with fp32 group scales
+    [32][16], then the step's 32 input ids."""
+    rec = 32 * 2048 + 32 * 16 * 4 + 32 * 4
+    raw = np.fromfile(path, np.uint8)
+    out = []
+    for s in range(len(raw) // rec):
+        r = raw[s * rec:(s + 1) * rec]
+        q = r[:65536].view(np.int8).astype(np.float32).reshape(32, 16, 128)
+        sc = r[65536:65536 + 2048].view(np.float32).reshape(32, 16, 1)
+        out.append((q * sc, q, r[65536 + 2048:].view(np.int32)))
+    return out
+
+
+def test_first_step_hidden_state_matches_the_reference_engine(tmp_path, capsys):
+    """One dense layer (a continuous function of the attention output): after a 3-block prefill pass and the first
+    denoising step over the cached prompt, the hidden state the readout sees differs between the two engines only by the
+    engine's own int8 re-quantisation of slightly different attention outputs: codes within a few steps, rel-L2 about
+    1.5e-2 (an int8 code step is 1/127 of a group's maximum)."""
+    dropin, ref_lib = os.path.join(REF, "libllada_dropin.so"), os.path.join(REF, "libllada_ref.so")
+    if not (os.path.exists(dropin) and os.path.exists(ref_lib)):
+        pytest.skip("oracle/_ref/libllada_{dropin,ref}.so not built (make -C oracle ref dropin REF=<reference checkout>)")
+    ed = importlib.import_module(PKG_NAME + ".engine_dir")
+    d = str(tmp_path / "dense")
+    ed.write_engine_dir(d, layers=1, dense_layers=1, vocab=VOCAB, seed=11)
+    run_engine(dropin, d, str(tmp_path / "mine.bin"))
+    run_engine(ref_lib, d, str(tmp_path / "ref.bin"))
+    mine, ref = hidden_states(str(tmp_path / "mine.bin")), hidden_states(str(tmp_path / "ref.bin"))
+    assert len(mine) >= 2 and len(ref) >= 2
+    (xa, qa, ia), (xb, qb, ib) = mine[0], ref[0]
+    assert np.array_equal(ia, ib) and int((ia == ed.MASK_ID).sum()) == 24
+    rel = float(np.linalg.norm(xa - xb) / np.linalg.norm(xb))
+    with capsys.disabled():
+        print(f"\n[engine, 1 dense layer] first step: hidden state rel-L2 {rel:.3e}, largest code difference "
+              f"{int(np.abs(qa - qb).max())}, codes equal {float((qa == qb).mean()):.3f}")
+    assert rel <= 3e-2 and np.abs(qa - qb).max() <= 6

@@ -107,7 +107,25 @@ def test_planner_covers_every_unit_once(api, lengths, nq, nctas):
     per_cta = [int(items[cta_first[c]:cta_first[c + 1], 4:6].sum()) for c in range(st.nctas)]
     assert max(per_cta) == st.max_cta_units
     if st.total_units >= 64 * nctas:                                         # enough work: shares are near equal
-        assert max(per_cta) <= 1.02 * st.total_units / st.nctas + 4
+        assert max(per_cta) <= 1.02 * st.total_units / st.nctas + 12         # (a cut never leaves a piece under 12 units)
+
+
+def test_planner_gives_every_run_its_own_cta_when_the_step_is_small(api):
+    """Fewer output tiles than CTAs: a run per CTA, tiles cut into equal runs of about sqrt(units) units; with more work
+    than that the shares are contiguous again and a tile straddles at most two CTAs' lists per cut."""
+    for nblocks, lo, hi in ((64, 6, 10), (256, 11, 17), (1024, 24, 37)):
+        st, items, cta_first = api.plan_preview([nblocks], 148)
+        assert st.nitems == st.nctas and np.all(np.diff(cta_first[:st.nctas + 1]) == 1)
+        per_tile = np.bincount(items[:, 7])
+        assert len(per_tile) == 4 and per_tile.min() == per_tile.max() and lo <= per_tile[0] <= hi, per_tile
+        units = items[:, 4] + items[:, 5]
+        assert units.max() - units[items[:, 5] == 0].min() <= 4 and np.all(items[:, 3] % api.tile_units() == 0)
+    st, items, cta_first = api.plan_preview([1024] * 30, 148)                 # 120 tiles of 1025 units on 148 CTAs
+    assert st.nctas == 148 and st.nitems > 148 and st.max_cta_units <= 1.02 * st.total_units / 148 + 12
+    st, items, cta_first = api.plan_preview([0, 1, 2, 3], 148)                # 16 tiny tiles: one CTA each
+    assert st.nctas == 16 and st.nitems == 16
+    st, items, cta_first = api.plan_preview([64] * 36, 148)                   # tiles of 65 units, shares of 64: no 1-unit runs
+    assert (items[:, 4] + items[:, 5]).min() >= 12
 
 
 def test_sharding_balances_ragged_requests(pkg):

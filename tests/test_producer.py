@@ -137,4 +137,4 @@ def test_producer_fused_with_commit(orc, pkg, nb, paged):
             torch.cuda.synchronize()
             assert torch.equal(ref, got)
     with pytest.raises(ValueError):
-        api.qkv_prepare_commit(args[0][:33], *args[1:], q1, k1, v1, got, max_blocks=maxb, blk=blk)
+        api.qkv_prepare_commit(args[0][:T - 1], *args[1:], q1, k1, v1, got, max_blocks=maxb, blk=blk)
