@@ -269,15 +269,20 @@ int llattn_kvpool_close(llattn_kvpool* pool, int32_t seq_id);
 /* out6 = pages, free, cached (reusable, unreferenced), block hits, block misses, evictions */
 int llattn_kvpool_stats(llattn_kvpool* pool, int64_t* out6);
 
-/* Self-test of the bounded waits every kernel here is built on, with nothing made to fail: one CTA whose four warps
- * wait on barriers that nothing will ever complete. Warp 0's limit is `limit_ns` (1 ns .. 100 ms); when it runs out
+/* Self-test of the bounded waits every kernel here is built on, with nothing made to fail: one CTA whose first four
+ * warps wait on barriers that nothing will ever complete and whose fifth waits on a counter nothing counts into (the
+ * wait of a CTA for the other runs of a split tile). Warp 0's limit is `limit_ns` (1 ns .. 100 ms); when it runs out
  * the warp raises the CTA's abort flag and the other warps, whose own limit is the kernels' two seconds, leave at their
- * next poll. The kernel returns normally; `err_word` (device int, zeroed by the caller) then holds bits 1|2|4|8 (one per
- * warp, the producer / dequant / MMA / softmax codes of llattn_device_status) and waited_ns4 (device, 4 x uint64) how
- * long each warp waited. No counterpart in the reference, whose kernels have no waits that can fail. */
-int llattn_wait_selftest(unsigned long long limit_ns, int* err_word, unsigned long long* waited_ns4, void* stream);
+ * next poll; the fifth warp then waits on its counter once more with `limit_ns` and lets that run out too. The kernel
+ * returns normally; `err_word` (device int, zeroed by the caller) then holds bits 1|2|4|8|128 (one per warp: the
+ * producer / dequant / MMA / softmax / fold codes of llattn_device_status) and waited_ns6 (device, 6 x uint64) how long
+ * each of the five warps waited, then how long the counter wait took to run out alone. No counterpart in the
+ * reference, whose kernels have no waits that can fail. */
+int llattn_wait_selftest(unsigned long long limit_ns, int* err_word, unsigned long long* waited_ns6, void* stream);
 
-/* Reads (and clears) the context's device error word; synchronises `stream`. 0 = no kernel wait ran out. */
+/* Reads (and clears) the context's device error word; synchronises `stream`. 0 = no kernel wait ran out. Bits: 1, 2, 4,
+ * 8 a producer / dequant / MMA-issue / softmax warp's wait inside a CTA, 16 the wait for the last MMA at the end of a CTA,
+ * 32 a malformed work item, 64 a misaligned shared-memory base, 128 a CTA's wait for the other runs of a tile it shares. */
 int llattn_device_status(llattn_ctx* ctx, void* stream, int* code);
 
 #ifdef __cplusplus

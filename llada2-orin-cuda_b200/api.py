@@ -153,8 +153,8 @@ def chunks_for(nblocks: int, bpc: int) -> int:
 
 
 def wait_selftest(limit_ns: int, err_word, waited_ns, stream=None) -> None:
-    """llattn_wait_selftest: four warps wait on barriers nothing completes; err_word (int32 [1]) and waited_ns
-    (int64 [4]) are device tensors."""
+    """llattn_wait_selftest: four warps wait on barriers nothing completes, a fifth on a counter nothing counts into;
+    err_word (int32 [1]) and waited_ns (int64 [6]) are device tensors."""
     _check(lib().llattn_wait_selftest(limit_ns, _ptr(err_word), _ptr(waited_ns), _stream(stream)))
 
 

@@ -303,12 +303,16 @@ extern "C" int llattn_attention_static(const void* Q, const void* Kf, const void
 
 // ====================================================================================================== wait self-test
 // What a kernel of this library does when a wait can never complete, shown without making any real kernel fail: four
-// warps wait on barriers nobody will ever arrive on. Warp 0 has `limit_ns` (a millisecond in the test); when its wait
-// runs out it raises the CTA's abort flag, as every role of the attention kernel does, and the other warps - whose own
-// limit is the kernels' two seconds - see the flag at their next poll and leave too. Every warp reports through the
-// error word, the kernel returns normally and the context stays usable.
+// warps wait on barriers nobody will ever arrive on, a fifth on a counter nobody counts into (the wait a CTA does for
+// the other runs of a split tile). Warp 0 has `limit_ns` (a millisecond in the test); when its wait runs out it raises
+// the CTA's abort flag, as every role of the attention kernel does, and the other warps - whose own limit is the
+// kernels' two seconds - see the flag at their next poll and leave too. Then the fifth warp waits on its counter once
+// more, alone and with the short limit, to show that wait running out by itself. Every warp reports through the error
+// word, the kernel returns normally and the context stays usable.
 namespace llattn {
-__global__ void __launch_bounds__(128) wait_selftest_kernel(unsigned long long limit_ns, int* err, unsigned long long* waited_ns) {
+__device__ int selftest_counter;       // nothing ever counts in here
+
+__global__ void __launch_bounds__(160) wait_selftest_kernel(unsigned long long limit_ns, int* err, unsigned long long* waited_ns) {
     __shared__ uint64_t bars[4];
     __shared__ int abort_flag;
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -319,20 +323,30 @@ __global__ void __launch_bounds__(128) wait_selftest_kernel(unsigned long long l
     }
     __syncthreads();
     const unsigned long long t0 = ptx::globaltimer_ns();
-    const bool ok = ptx::mbar_wait_limit(ptx::smem_u32(&bars[warp]), 0, &abort_flag, warp == 0 ? limit_ns : ptx::WAIT_LIMIT_NS);
+    bool ok;
+    if (warp < 4) ok = ptx::mbar_wait_limit(ptx::smem_u32(&bars[warp]), 0, &abort_flag, warp == 0 ? limit_ns : ptx::WAIT_LIMIT_NS);
+    else ok = wait_count(&selftest_counter, 1, &abort_flag, ptx::WAIT_LIMIT_NS);      // the wait of the tile folding: released by the flag
     const unsigned long long t1 = ptx::globaltimer_ns();
     if (!ok && lane == 0) {
-        atomicOr(err, warp == 0 ? ERR_WAIT_PRODUCER : warp == 1 ? ERR_WAIT_DEQUANT : warp == 2 ? ERR_WAIT_MMA : ERR_WAIT_SOFTMAX);
+        atomicOr(err, warp == 0 ? ERR_WAIT_PRODUCER : warp == 1 ? ERR_WAIT_DEQUANT : warp == 2 ? ERR_WAIT_MMA : warp == 3 ? ERR_WAIT_SOFTMAX : ERR_WAIT_FOLD);
         waited_ns[warp] = t1 - t0;
     }
     __syncthreads();
+    // and the counter wait running out by itself, with the short limit
+    if (warp == 4) {
+        abort_flag = 0;
+        __syncwarp();
+        const unsigned long long t2 = ptx::globaltimer_ns();
+        const bool ok2 = wait_count(&selftest_counter, 1, &abort_flag, limit_ns);
+        if (!ok2 && lane == 0) waited_ns[5] = ptx::globaltimer_ns() - t2;
+    }
 }
 }  // namespace llattn
 
-extern "C" int llattn_wait_selftest(unsigned long long limit_ns, int* err_word, unsigned long long* waited_ns4, void* stream) {
-    if (!err_word || !waited_ns4) return fail(LLATTN_EINVAL, "wait_selftest: null pointer");
+extern "C" int llattn_wait_selftest(unsigned long long limit_ns, int* err_word, unsigned long long* waited_ns6, void* stream) {
+    if (!err_word || !waited_ns6) return fail(LLATTN_EINVAL, "wait_selftest: null pointer");
     if (limit_ns == 0 || limit_ns > 100000000ull) return fail(LLATTN_EINVAL, "wait_selftest: limit of %llu ns; 1 ns .. 100 ms", limit_ns);
-    llattn::wait_selftest_kernel<<<1, 128, 0, as_stream(stream)>>>(limit_ns, err_word, waited_ns4);
+    llattn::wait_selftest_kernel<<<1, 160, 0, as_stream(stream)>>>(limit_ns, err_word, waited_ns6);
     CU(cudaGetLastError());
     return LLATTN_OK;
 }

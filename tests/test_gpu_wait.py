@@ -1,6 +1,7 @@
 """A wait that can never complete ends in an error code, not in a hang.
 
-Every wait in this library's kernels is an mbarrier wait with a time limit (two seconds in the real kernels); when one
+Every wait in this library's kernels has a time limit (two seconds in the real kernels), the mbarrier waits inside a
+CTA as well as a CTA's wait for the other runs of a tile it shares; when one
 runs out the role raises the CTA's abort flag, every other role leaves at its next poll, the kernel reports through the
 device error word and returns. llattn_wait_selftest shows exactly that chain on a kernel of its own, with a
 one-millisecond limit and barriers that nothing ever completes: no real kernel is made to fail, nothing faults, the
@@ -18,13 +19,14 @@ def test_wait_runs_out_with_an_error_code_and_the_context_stays_usable(pkg, orc)
     api = importlib.import_module(pkg.__name__ + ".api")
     api.lib()
     err = torch.zeros(1, dtype=torch.int32, device="cuda")
-    waited = torch.zeros(4, dtype=torch.int64, device="cuda")
+    waited = torch.zeros(6, dtype=torch.int64, device="cuda")
     api.wait_selftest(1_000_000, err, waited)
     torch.cuda.synchronize()
-    assert int(err.item()) == 1 | 2 | 4 | 8                    # every warp left through the error path
+    assert int(err.item()) == 1 | 2 | 4 | 8 | 128              # every warp left through the error path
     w = waited.cpu().numpy()
     assert 0.9e6 <= w[0] <= 20e6                               # the short limit ran out where it should
-    assert (w[1:] >= 0.9e6).all() and (w[1:] <= 50e6).all()    # the others were released by the abort flag, far below their 2 s
+    assert (w[1:5] >= 0.9e6).all() and (w[1:5] <= 50e6).all()  # the others were released by the abort flag, far below their 2 s
+    assert 0.9e6 <= w[5] <= 20e6                               # the wait for a split tile's other runs, running out alone
     with pytest.raises(api.LlattnError):
         api.wait_selftest(0, err, waited)
     # the device is fine: a normal attention call on the same context of this process
