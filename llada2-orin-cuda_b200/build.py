@@ -25,8 +25,10 @@ def build(force: bool = False, verbose: bool = False) -> str:
     if not force and os.path.exists(LIB) and all(os.path.getmtime(LIB) >= os.path.getmtime(s) for s in srcs):
         return LIB
     nvcc = os.environ.get("NVCC", "nvcc")
-    cmd = [nvcc] + NVCC_FLAGS + (["-Xptxas", "-v"] if verbose else []) + [os.path.join(CSRC, "llattn.cu"), "-o", LIB]
+    tmp = LIB + ".building"                      # the library appears in one step: a reader never sees half a file
+    cmd = [nvcc] + NVCC_FLAGS + (["-Xptxas", "-v"] if verbose else []) + [os.path.join(CSRC, "llattn.cu"), "-o", tmp]
     subprocess.check_call(cmd)
+    os.replace(tmp, LIB)
     return LIB
 
 

@@ -84,7 +84,8 @@ constexpr int SM_V = SM_K + 2 * TILE_BYTES;        // two V tiles
 constexpr int SM_RAW = SM_V + 2 * VTILE_BYTES;
 constexpr int SM_BAR = SM_RAW + NRAW * RAW_STRIDE;
 constexpr int SM_MISC = SM_BAR + 512;
-constexpr int ATTN_SMEM_BYTES = SM_MISC + 16;
+constexpr int SM_FIRST = SM_MISC + 16;             // the CTA's first run descriptor (64 bytes), fetched during set-up
+constexpr int ATTN_SMEM_BYTES = SM_FIRST + 64;
 // warps 0-3 softmax (warp w: TMEM lanes 32 w .. 32 w + 31, one query row per thread), 4-11 dequant (four groups of two
 // warps, group g takes unit g of every tile: a thread's scale / minimum words then serve eight passes over the record),
 // then the service warps. Every scheduler carries one softmax warp, two dequantising warps and one service warp.
@@ -125,8 +126,7 @@ static_assert((GROUP_WARPS == 2 || GROUP_WARPS == 4) && DEQUANT_WARPS % GROUP_WA
               "dequant warps: groups of two or four, 1, 2 or 4 groups");
 
 struct KParams {
-    const SeqDesc* seqs;           // list mode
-    const WorkItem* items;
+    const RunDesc* items;          // list mode: runs in plan order, each with its sequence; nullptr = reference-grid mode
     const int32_t* cta_first;      // [gridDim.x + 1]
     const half* Q;
     const half* Kf;
@@ -148,10 +148,15 @@ struct KParams {
     int ref_nchunks;
 };
 
-__device__ __forceinline__ bool fetch_item(const KParams& p, int idx, WorkItem& w, SeqDesc& s) {
+__device__ __forceinline__ bool fetch_item(const KParams& p, int idx, WorkItem& w, SeqDesc& s, const RunDesc* first, int first_idx) {
     if (p.items) {
-        w = p.items[idx];
-        s = p.seqs[w.seq];
+        const uint4* src = reinterpret_cast<const uint4*>(idx == first_idx ? first : p.items + idx);   // the first one is in shared memory
+        RunDesc r;
+        uint4* dst = reinterpret_cast<uint4*>(&r);
+#pragma unroll
+        for (int k = 0; k < 4; ++k) dst[k] = src[k];
+        w = r.w;
+        s = r.s;
         s.cache += p.cache_offset;
         return true;
     }
@@ -494,6 +499,10 @@ __device__ __forceinline__ void attn_tile_body(const KParams& p, const int cta) 
         ptx::fence_mbar_init();
         *abort_flag = 0;
     }
+    // the first run's descriptor comes in while the barriers and tensor memory are being set up
+    const RunDesc* first_run = reinterpret_cast<const RunDesc*>(smem + SM_FIRST);
+    if (p.items && i0 < i1 && warp == 1 && lane < 16)
+        reinterpret_cast<uint32_t*>(smem + SM_FIRST)[lane] = __ldg(reinterpret_cast<const uint32_t*>(p.items + i0) + lane);
     if (warp == WARP_MMA) { ptx::tmem_alloc(ptx::smem_u32(tmem_slot), TMEM_COLS); ptx::tmem_relinquish(); }
     ptx::tc_fence_before();
     __syncthreads();
@@ -520,7 +529,7 @@ __device__ __forceinline__ void attn_tile_body(const KParams& p, const int cta) 
 #pragma unroll 1
         for (int ii = i0; ii < i1 && alive; ++ii) {
             WorkItem w; SeqDesc s;
-            if (!fetch_item(p, ii, w, s)) continue;
+            if (!fetch_item(p, ii, w, s, first_run, i0_any)) continue;
             const int U = w.rec_count + w.fresh, ntiles = (U + TILE_UNITS - 1) / TILE_UNITS;
             // Reference exponent of the row, log2 units: the exact maximum of the run's first tile (a row dominated by a
             // key of that tile then has p = 1 for it, without rounding); it moves only when a later score exceeds it by
@@ -619,6 +628,9 @@ __device__ __forceinline__ void attn_tile_body(const KParams& p, const int cta) 
                         *reinterpret_cast<float4*>(orow + 32 * c + 8 * g + 4) = hi;
                     }
                 }
+                // the accumulator has been read: the next run's PV may start while the stores below drain
+                ptx::tc_fence_before();
+                ptx::mbar_arrive(BAR(B_O_FREE));
                 p.Lpart[size_t(w.slot) * QR + row] = lsum;
                 p.Mpart[size_t(w.slot) * QR + row] = mref;
                 if (fused) {                   // this warp's 32 rows of the run are out: count it in
@@ -658,9 +670,9 @@ __device__ __forceinline__ void attn_tile_body(const KParams& p, const int cta) 
                     row_store(p.out, ro, c, v);
                 }
                 row_finish(p.out, ro, M, den);
+                ptx::tc_fence_before();
+                ptx::mbar_arrive(BAR(B_O_FREE));
             }
-            ptx::tc_fence_before();
-            ptx::mbar_arrive(BAR(B_O_FREE));
         }
     } else if (warp < WARP_SERVICE) {
         // ================================================================== dequant: records -> fp16 operand tiles
@@ -679,7 +691,7 @@ __device__ __forceinline__ void attn_tile_body(const KParams& p, const int cta) 
 #pragma unroll 1
         for (int ii = i0; ii < i1 && alive; ++ii) {
             WorkItem w; SeqDesc s;
-            if (!fetch_item(p, ii, w, s)) continue;
+            if (!fetch_item(p, ii, w, s, first_run, i0_any)) continue;
             const int U = w.rec_count + w.fresh, ntiles = (U + TILE_UNITS - 1) / TILE_UNITS;
             const size_t f0 = (size_t(s.q_first + w.qblk) * BLK) * NKV * D + size_t(w.kvh) * D;
             int i = 0;
@@ -774,7 +786,7 @@ __device__ __forceinline__ void attn_tile_body(const KParams& p, const int cta) 
 #pragma unroll 1
         for (int ii = i0; ii < i1 && alive; ++ii) {
             WorkItem w; SeqDesc s;
-            if (!fetch_item(p, ii, w, s)) continue;
+            if (!fetch_item(p, ii, w, s, first_run, i0_any)) continue;
             const size_t hbase = size_t(w.kvh) * s.head_stride;
 #pragma unroll 1
             for (uint32_t u = (pk - r0) % PRODUCERS; u < uint32_t(w.rec_count); u += PRODUCERS) {
@@ -828,7 +840,7 @@ __device__ __forceinline__ void attn_tile_body(const KParams& p, const int cta) 
 #pragma unroll 1
         for (int ii = i0; ii < i1 && alive; ++ii) {
             WorkItem w; SeqDesc s;
-            if (!uniform_i32(fetch_item(p, ii, w, s))) continue;
+            if (!uniform_i32(fetch_item(p, ii, w, s, first_run, i0_any))) continue;
             const int U = uniform_i32(w.rec_count + w.fresh), ntiles = (U + TILE_UNITS - 1) / TILE_UNITS;
             if (!uniform_i32(ptx::mbar_wait(BAR(B_Q_FULL), itc & 1, abort_flag))) { alive = false; errbits |= ERR_WAIT_MMA; break; }
             for (int j = 0; j < 2 && j < ntiles && alive; ++j)
@@ -875,7 +887,7 @@ __device__ __forceinline__ void attn_tile_body(const KParams& p, const int cta) 
 #pragma unroll 1
         for (int ii = i0; ii < i1 && alive; ++ii) {
             WorkItem w; SeqDesc s;
-            if (!uniform_i32(fetch_item(p, ii, w, s))) continue;
+            if (!uniform_i32(fetch_item(p, ii, w, s, first_run, i0_any))) continue;
             const int U = uniform_i32(w.rec_count + w.fresh), ntiles = (U + TILE_UNITS - 1) / TILE_UNITS;
             if (!uniform_i32(ptx::mbar_wait(BAR(B_Q_FULL), itc & 1, abort_flag))) { alive = false; errbits |= ERR_WAIT_MMA; break; }
 #pragma unroll 1
@@ -917,7 +929,7 @@ __device__ __forceinline__ void attn_tile_body(const KParams& p, const int cta) 
 #pragma unroll 1
         for (int ii = i0; ii < i1 && alive; ++ii) {
             WorkItem w; SeqDesc s;
-            if (!uniform_i32(fetch_item(p, ii, w, s))) continue;
+            if (!uniform_i32(fetch_item(p, ii, w, s, first_run, i0_any))) continue;
             const int U = uniform_i32(w.rec_count + w.fresh), ntiles = (U + TILE_UNITS - 1) / TILE_UNITS;
 #pragma unroll 1
             for (int i = 0; i < ntiles; ++i, ++t) {
@@ -972,7 +984,7 @@ __device__ __forceinline__ void attn_tile_body(const KParams& p, const int cta) 
 #pragma unroll 1
         for (int ii = i0_any; ii < i1_any; ++ii) {
             WorkItem w; SeqDesc sq;
-            if (!fetch_item(p, ii, w, sq)) continue;
+            if (!fetch_item(p, ii, w, sq, first_run, i0_any)) continue;
             const MergeDesc md = p.merge[w.tile];
             if (md.nslots <= 1) continue;
             int* counters = p.tile_counters + 4 * w.tile;

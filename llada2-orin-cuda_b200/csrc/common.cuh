@@ -37,6 +37,14 @@ struct WorkItem {
     int32_t tile;             // output tile (query block x kv head) the run belongs to: index of its MergeDesc
 };
 
+// What the kernel reads per run: the run and its sequence side by side, 64 bytes, so that a CTA reaches everything about
+// its first run with two dependent loads (its item range, then this) instead of three.
+struct alignas(16) RunDesc {
+    WorkItem w;
+    SeqDesc s;
+};
+static_assert(sizeof(RunDesc) == 64, "RunDesc layout");
+
 // One output tile (query block x kv head) and the partial slots that make it up.
 struct MergeDesc {
     int32_t q_index;          // global query block index (q_first + qblk)

@@ -71,7 +71,7 @@ struct llattn_plan {
     cudaEvent_t ev_upload = nullptr;
     bool upload_pending = false;
     const llattn::SeqDesc* d_seqs = nullptr;
-    const llattn::WorkItem* d_items = nullptr;
+    const llattn::RunDesc* d_items = nullptr;
     const int32_t* d_cta_first = nullptr;
     const llattn::MergeDesc* d_merge = nullptr;
 };

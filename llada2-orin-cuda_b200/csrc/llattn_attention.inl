@@ -292,7 +292,8 @@ int stage_plan(llattn_plan* pl, const HostPlan& hp) {
                     hp.seqs.size(), hp.items.size(), hp.merge.size(), pl->cap_seqs, pl->cap_items, pl->cap_tiles);
     uint8_t* h = static_cast<uint8_t*>(pl->host_blob);
     memcpy(h + pl->off_seqs, hp.seqs.data(), hp.seqs.size() * sizeof(llattn::SeqDesc));
-    memcpy(h + pl->off_items, hp.items.data(), hp.items.size() * sizeof(llattn::WorkItem));
+    llattn::RunDesc* runs = reinterpret_cast<llattn::RunDesc*>(h + pl->off_items);
+    for (size_t i = 0; i < hp.items.size(); ++i) runs[i] = llattn::RunDesc{hp.items[i], hp.seqs[hp.items[i].seq]};
     memcpy(h + pl->off_cta, hp.cta_first.data(), hp.cta_first.size() * sizeof(int32_t));
     memcpy(h + pl->off_merge, hp.merge.data(), hp.merge.size() * sizeof(llattn::MergeDesc));
     return LLATTN_OK;
@@ -325,7 +326,7 @@ int llattn_plan_create(llattn_ctx* c, const llattn_seq* seqs, int nseq, int ncta
     pl->cap_items = hp.merge.size() + size_t(nctas);
     pl->off_seqs = 0;
     pl->off_items = pl->off_seqs + up256(pl->cap_seqs * sizeof(SeqDesc));
-    pl->off_cta = pl->off_items + up256(pl->cap_items * sizeof(WorkItem));
+    pl->off_cta = pl->off_items + up256(pl->cap_items * sizeof(RunDesc));
     pl->off_merge = pl->off_cta + up256((size_t(nctas) + 1) * sizeof(int32_t));
     pl->blob_bytes = pl->off_merge + up256(pl->cap_tiles * sizeof(MergeDesc));
     auto bail = [&](int code, const char* what) {
@@ -344,7 +345,7 @@ int llattn_plan_create(llattn_ctx* c, const llattn_seq* seqs, int nseq, int ncta
     if (cudaMemcpy(pl->dev_blob, pl->host_blob, pl->blob_bytes, cudaMemcpyHostToDevice) != cudaSuccess) return bail(LLATTN_ECUDA, "upload failed");
     const uint8_t* d = static_cast<const uint8_t*>(pl->dev_blob);
     pl->d_seqs = reinterpret_cast<const SeqDesc*>(d + pl->off_seqs);
-    pl->d_items = reinterpret_cast<const WorkItem*>(d + pl->off_items);
+    pl->d_items = reinterpret_cast<const RunDesc*>(d + pl->off_items);
     pl->d_cta_first = reinterpret_cast<const int32_t*>(d + pl->off_cta);
     pl->d_merge = reinterpret_cast<const MergeDesc*>(d + pl->off_merge);
     fill_stats(pl, hp, nseq);
@@ -431,7 +432,7 @@ int llattn_attention(llattn_ctx* c, const llattn_plan* pl, const llattn_io* io, 
     float* Mpart = Opart + ns * QR * D;
     float* Lpart = Mpart + ns * QR;
     KParams p{};
-    p.seqs = pl->d_seqs; p.items = pl->d_items; p.cta_first = pl->d_cta_first;
+    p.items = pl->d_items; p.cta_first = pl->d_cta_first;
     p.Q = static_cast<const half*>(io->Q); p.Kf = static_cast<const half*>(io->Kf); p.Vf = static_cast<const half*>(io->Vf);
     p.Opart = Opart; p.Mpart = Mpart; p.Lpart = Lpart;
     p.sl2 = (io->scale > 0.f ? io->scale : 0.08838834764831845f) * 1.4426950408889634f;
