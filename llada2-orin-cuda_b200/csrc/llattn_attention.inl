@@ -56,9 +56,8 @@ void finish_plan(HostPlan& hp, int nctas) {
 }
 
 // Contiguous shares of the flattened unit sequence (see above).
-void cut_contiguous(const llattn_seq* seqs, int nseq, int nctas, int64_t total, HostPlan& hp) {
+void cut_contiguous(const llattn_seq* seqs, int nseq, int nctas, int64_t total, int64_t MIN_UNITS, HostPlan& hp) {
     using namespace llattn;
-    constexpr int64_t MIN_UNITS = 16;
     // The share of the CTA being filled is re-derived from what is left (units and CTAs), so rounding a cut down to a
     // tile boundary never pushes work into an extra CTA: the plan uses at most `nctas` CTAs.
     int64_t left = total;
@@ -163,14 +162,22 @@ int build_plan(const llattn_seq* seqs, int nseq, int nctas, HostPlan& hp) {
     }
     hp.total_units = total;
     hp.nq_total = nq_total;
-    cut_contiguous(seqs, nseq, nctas, total, hp);
-    if (ntile_out <= nctas) {
-        HostPlan alt;
-        cut_per_tile(seqs, nseq, nctas, total, alt);
+    auto take_if_cheaper = [&](HostPlan& alt) {
         if (alt.max_cta_cost < hp.max_cta_cost) {
             hp.items.swap(alt.items); hp.cta_first.swap(alt.cta_first); hp.merge.swap(alt.merge);
             hp.used_ctas = alt.used_ctas; hp.max_cta_units = alt.max_cta_units; hp.max_cta_cost = alt.max_cta_cost;
         }
+    };
+    cut_contiguous(seqs, nseq, nctas, total, 16, hp);
+    if (total < 16 * int64_t(nctas)) {       // little work: shorter shares on more CTAs may beat several runs per CTA
+        HostPlan alt;
+        cut_contiguous(seqs, nseq, nctas, total, TILE_UNITS, alt);
+        take_if_cheaper(alt);
+    }
+    if (ntile_out <= nctas) {
+        HostPlan alt;
+        cut_per_tile(seqs, nseq, nctas, total, alt);
+        take_if_cheaper(alt);
     }
     return LLATTN_OK;
 }
