@@ -399,6 +399,26 @@ class Step:
         return e0.elapsed_time(e1)
 
 
+def bind_to_nvml_cpu_set(R, node):
+    """The CPUs NVML names as closest to this rank's GPU (nvmlDeviceGetCpuAffinity), if that is a proper subset of
+    the CPUs this process may use."""
+    try:
+        import pynvml
+        pynvml.nvmlInit()
+        h = pynvml.nvmlDeviceGetHandleByPciBusId(R.pci.encode() if isinstance(R.pci, str) else R.pci)
+        ncpu = max(os.sched_getaffinity(0)) + 1
+        words = pynvml.nvmlDeviceGetCpuAffinity(h, (ncpu + 63) // 64)
+        cpus = {64 * i + b for i, w in enumerate(words) for b in range(64) if (int(w) >> b) & 1}
+        mine = set(os.sched_getaffinity(0))
+        allowed = cpus & mine
+        if not allowed or allowed == mine:
+            return {"numa_node": node, "bound": False, "nvml_cpus": len(cpus)}
+        os.sched_setaffinity(0, allowed)
+        return {"numa_node": node, "bound": True, "cpus": len(allowed), "source": "nvml cpu affinity"}
+    except Exception as e:                             # noqa: BLE001 - best effort, reported
+        return {"numa_node": node, "bound": False, "nvml": type(e).__name__}
+
+
 def bind_to_gpu_numa_node(R):
     """Best effort: run this rank's host threads on the CPUs of its GPU's NUMA node before pinned buffers are allocated
     (first touch then places them there). Returns what was done, for the JSON line."""
@@ -407,8 +427,8 @@ def bind_to_gpu_numa_node(R):
     try:
         dom, rest = R.pci.split(":", 1)
         node = int(open(f"/sys/bus/pci/devices/{dom[-4:].lower()}:{rest.lower()}/numa_node").read())
-        if node < 0:
-            return {"numa_node": node, "bound": False}
+        if node < 0:                                   # no topology in sysfs (virtualised): ask the driver for the GPU's CPUs
+            return bind_to_nvml_cpu_set(R, node)
         cpus = set()
         for part in open(f"/sys/devices/system/node/node{node}/cpulist").read().strip().split(","):
             lo, _, hi = part.partition("-")
