@@ -266,6 +266,30 @@ __device__ __forceinline__ float rowmax16(const uint32_t (&r)[16]) {
     }
     return max3(max3(a, b, __uint_as_float(r[7])), __uint_as_float(r[15]), __uint_as_float(r[15]));
 }
+#ifndef LLATTN_POLY_MOD
+#define LLATTN_POLY_MOD 0      // n > 0: every n-th score pair takes its 2^x from the multiply-add pipes instead of the MUFU
+#endif
+// 2^x for two values on the multiply-add pipes: x is held above -125, split into round(x) and a fraction in [-0.5, 0.5]
+// by the add-a-large-constant trick, 2^fraction comes from a degree-4 polynomial (relative error 2e-6, far below the
+// fp16 rounding that follows) and round(x) is added into the exponent field.
+__device__ __forceinline__ void exp2_pair_poly(float x0, float x1, float& e0, float& e1) {
+    x0 = fmaxf(x0, -125.f); x1 = fmaxf(x1, -125.f);
+    unsigned long long x, t, n, f, q;
+    asm("mov.b64 %0, {%1, %2};" : "=l"(x) : "f"(x0), "f"(x1));
+    asm("{\n\t.reg .b64 m;\n\tmov.b64 m, 0x4b4000004b400000;\n\tadd.rn.f32x2 %0, %1, m;\n\t}" : "=l"(t) : "l"(x));        // 1.5 * 2^23 + round(x)
+    asm("{\n\t.reg .b64 m;\n\tmov.b64 m, 0xcb400000cb400000;\n\tadd.rn.f32x2 %0, %1, m;\n\t}" : "=l"(n) : "l"(t));        // round(x)
+    asm("{\n\t.reg .b64 m;\n\tmov.b64 m, 0xbf800000bf800000;\n\tfma.rn.f32x2 %0, %1, m, %2;\n\t}" : "=l"(f) : "l"(n), "l"(x));   // x - round(x)
+    asm("{\n\t.reg .b64 a, b;\n\tmov.b64 a, 0x3c1803f73c1803f7;\n\tmov.b64 b, 0x3d64d2b93d64d2b9;\n\tfma.rn.f32x2 %0, %1, a, b;\n\t}" : "=l"(q) : "l"(f));   // 0.009278289 f + 0.055865023
+    asm("{\n\t.reg .b64 c;\n\tmov.b64 c, 0x3e76138d3e76138d;\n\tfma.rn.f32x2 %0, %0, %1, c;\n\t}" : "+l"(q) : "l"(f));                              // 0.24030896
+    asm("{\n\t.reg .b64 c;\n\tmov.b64 c, 0x3f3170f03f3170f0;\n\tfma.rn.f32x2 %0, %0, %1, c;\n\t}" : "+l"(q) : "l"(f));                              // 0.69312954
+    asm("{\n\t.reg .b64 c;\n\tmov.b64 c, 0x3f7fffdc3f7fffdc;\n\tfma.rn.f32x2 %0, %0, %1, c;\n\t}" : "+l"(q) : "l"(f));                              // 0.99999785
+    uint32_t q0, q1, t0, t1;
+    asm("mov.b64 {%0, %1}, %2;" : "=r"(q0), "=r"(q1) : "l"(q));
+    asm("mov.b64 {%0, %1}, %2;" : "=r"(t0), "=r"(t1) : "l"(t));
+    e0 = __uint_as_float(q0 + (t0 << 23));
+    e1 = __uint_as_float(q1 + (t1 << 23));
+}
+
 // Score pairs J0 .. J1-1 of 16 scores -> packed fp16 p. PRECISE: also the fp16 remainder p - fp16(p) (exact in fp32, then
 // rounded once more: together the pair carries p to about 22 bits).
 template <int J0, int J1, bool PRECISE>
@@ -275,7 +299,9 @@ __device__ __forceinline__ void exp_pairs16(const uint32_t (&r)[16], uint32_t* p
         if (LLATTN_SKIP & 2) { pk[j] = r[2 * j] & 0x03ff03ffu; continue; }
         float x0, x1;
         fma2(r[2 * j], r[2 * j + 1], sl2x2, nm2, x0, x1);
-        const float e0 = ex2(x0), e1 = ex2(x1);
+        float e0, e1;
+        if (LLATTN_POLY_MOD > 0 && j % LLATTN_POLY_MOD == LLATTN_POLY_MOD - 1) exp2_pair_poly(x0, x1, e0, e1);
+        else { e0 = ex2(x0); e1 = ex2(x1); }
         const half2 h = __floats2half2_rn(e0, e1);
         pk[j] = *reinterpret_cast<const uint32_t*>(&h);
         if (PRECISE) {
