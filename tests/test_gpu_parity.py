@@ -240,6 +240,27 @@ def test_ragged_batch_and_forced_splits(api, ctx, orc, pkg):
         assert np.abs(res["LSE"] - Lw).max() <= TOL_LSE
 
 
+@pytest.mark.parametrize("nblocks,nctas,per_tile", [(60, 8, 2), (60, 12, 3), (60, 16, 4), (120, 28, 7), (150, 60, 10)])
+def test_tiles_cut_into_n_runs_are_folded_by_their_ctas(api, ctx, orc, pkg, nblocks, nctas, per_tile):
+    """One sequence on a chosen number of CTAs: every tile is cut into the same number of runs, each on a CTA of its own,
+    and the tile is folded by those CTAs together (2, 3 and 4 runs take the few-slots path, more the general one). Every
+    output form is checked, and the fold is independent of who finishes when: two launches give the same bits."""
+    Q, Kf, Vf, cache, maxb = make_case(pkg.workload, orc, nblocks, seq=400 + nctas)
+    case = [(Q, Kf, Vf, cache, maxb, nblocks)]
+    res = run_batched(api, ctx, case, want=("O32", "O16", "LSE", "q8"), nctas=nctas)
+    assert res["stats"].nitems == 4 * per_tile and res["stats"].nctas == 4 * per_tile
+    Ow, Lw = orc.attention(Q, Kf, Vf, cache, maxb, nblocks, dq_mode=1)
+    assert relmax(res["O32"], Ow) <= tol_o(nblocks) and rel_l2(res["O32"], Ow) <= TOL_L2
+    assert np.abs(res["LSE"] - Lw).max() <= TOL_LSE
+    assert np.array_equal(res["O16"], res["O32"].astype(np.float16))
+    q8, s8, sum8 = orc.act_q8(res["O32"])
+    assert np.array_equal(res["q8"], q8) and np.array_equal(res["s8"], s8) and np.array_equal(res["sum8"], sum8)
+    again = run_batched(api, ctx, case, want=("O32", "LSE"), nctas=nctas)
+    assert np.array_equal(again["O32"], res["O32"]) and np.array_equal(again["LSE"], res["LSE"])
+    one = run_batched(api, ctx, case, want=("O32",), nctas=4)          # one run per tile: no folding at all
+    assert one["stats"].nitems == 4 and rel_l2(one["O32"], res["O32"]) <= 2 * TOL_L2
+
+
 def test_many_short_items_per_cta(api, ctx, orc, pkg):
     """48 short sequences on 5 CTAs: every CTA walks about 40 items, so the per-item hand-overs (query rows into tensor
     memory, accumulator release, partial slots) run back to back, with tiles of 1 to 4 units."""
