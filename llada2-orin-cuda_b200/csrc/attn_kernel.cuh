@@ -300,7 +300,7 @@ __device__ __forceinline__ void exp_pairs16(const uint32_t (&r)[16], uint32_t* p
         float x0, x1;
         fma2(r[2 * j], r[2 * j + 1], sl2x2, nm2, x0, x1);
         float e0, e1;
-        if (LLATTN_POLY_MOD > 0 && j % LLATTN_POLY_MOD == LLATTN_POLY_MOD - 1) exp2_pair_poly(x0, x1, e0, e1);
+        if (LLATTN_POLY_MOD > 0 && j % (LLATTN_POLY_MOD > 0 ? LLATTN_POLY_MOD : 1) == LLATTN_POLY_MOD - 1) exp2_pair_poly(x0, x1, e0, e1);
         else { e0 = ex2(x0); e1 = ex2(x1); }
         const half2 h = __floats2half2_rn(e0, e1);
         pk[j] = *reinterpret_cast<const uint32_t*>(&h);
@@ -1005,8 +1005,10 @@ __device__ __forceinline__ void attn_tile_body(const KParams& p, const int cta) 
     // ---- split tiles. Every run of this CTA is stored and counted by now, so nothing this CTA waits for depends on
     // this CTA: for each of its runs that is part of a split tile, wait (bounded) until all of the tile's runs are
     // counted in, then all sixteen warps finish this run's share of the rows, a warp per row. The last warp to leave a
-    // tile puts both of its counters back to zero for the next launch.
+    // tile puts both of its counters back to zero for the next launch. Every thread of the CTA walks this loop the same
+    // way (same runs, same outcome), so the CTA barrier inside it is reached by all.
     if (p.merge != nullptr) {
+        int nsplit = 0;
 #pragma unroll 1
         for (int ii = i0_any; ii < i1_any; ++ii) {
             WorkItem w; SeqDesc sq;
@@ -1014,7 +1016,16 @@ __device__ __forceinline__ void attn_tile_body(const KParams& p, const int cta) 
             const MergeDesc md = p.merge[w.tile];
             if (md.nslots <= 1) continue;
             int* counters = p.tile_counters + 4 * w.tile;
-            if (!wait_count(counters, SOFTMAX_WARPS * md.nslots, abort_flag, ptx::WAIT_LIMIT_NS)) {
+            // one warp polls the counter for the whole CTA (hundreds of finished CTAs polling with every warp would load
+            // the L2 the slower CTAs still stream through); the others learn the outcome through shared memory
+            volatile int* outcome = reinterpret_cast<volatile int*>(smem + SM_MISC + 8) + (nsplit & 1);
+            if (warp == 0) {
+                const bool ok = wait_count(counters, SOFTMAX_WARPS * md.nslots, abort_flag, ptx::WAIT_LIMIT_NS);
+                if (lane == 0) *outcome = ok;
+            }
+            __syncthreads();
+            ++nsplit;
+            if (!*outcome) {
                 errbits |= ERR_WAIT_FOLD;
                 *abort_flag = 1;
                 break;
