@@ -34,7 +34,7 @@ struct HostPlan {
 // What a CTA's list costs, in the time of a unit (about a third of a microsecond): its units, a start-up charge per run
 // (query load, first records, the pipeline filling up, the epilogue), and for a run of a split tile the partial result's
 // round trip through the L2 and its share of the folding.
-constexpr int64_t RUN_STARTUP_UNITS = 20, RUN_SPLIT_UNITS = 6;
+constexpr int64_t RUN_STARTUP_UNITS = 20, RUN_SPLIT_UNITS = 4;
 // A piece of a tile shorter than this is not worth a run of its own: the cut moves to the tile's end (or start) instead.
 constexpr int SHORTEST_PIECE = 12;
 
@@ -103,7 +103,7 @@ void cut_contiguous(const llattn_seq* seqs, int nseq, int nctas, int64_t total, 
 }
 
 // Every run on a CTA of its own: each output tile is cut into equal runs, their number in proportion to the tile's
-// length (and no run shorter than about sqrt(units of the tile)). Possible when there are no more output tiles than CTAs; better
+// length (and no run shorter than about 0.75 sqrt(units of the tile)). Possible when there are no more output tiles than CTAs; better
 // than contiguous shares when the step is a latency problem (a handful of sequences), because no CTA then pays the
 // start-up of two runs one after the other.
 void cut_per_tile(const llattn_seq* seqs, int nseq, int nctas, int64_t total, HostPlan& hp) {
@@ -114,9 +114,10 @@ void cut_per_tile(const llattn_seq* seqs, int nseq, int nctas, int64_t total, Ho
         for (int j = 0; j < seqs[s].nq; ++j)
             for (int h = 0; h < NKV; ++h) {
                 const int64_t U = seqs[s].nblocks + j + 1;
-                // a run costs about a unit's time per unit plus one and a quarter units per run of its tile (its partial
-                // result is written, waited for and read back): the sum is smallest near sqrt(U) units per run
-                const int64_t shortest = std::max<int64_t>(TILE_UNITS, int64_t(1.1 * std::sqrt(double(U)) + 0.5));
+                // a run costs about a unit's time per unit plus a bit over half a unit per run of its tile (its partial
+                // result is written, waited for and read back): the sum is smallest near 0.75 sqrt(U) units per run
+                // (measured: 8 units at 2 K tokens, 12 at 8 K)
+                const int64_t shortest = std::max<int64_t>(2 * TILE_UNITS, int64_t(0.75 * std::sqrt(double(U)) + 0.5));
                 const int64_t by_share = U * nctas / total, by_length = (U + shortest - 1) / shortest;
                 runs.push_back(int(std::max<int64_t>(1, std::min(by_share, by_length))));
                 given += runs.back();

@@ -240,7 +240,7 @@ def test_ragged_batch_and_forced_splits(api, ctx, orc, pkg):
         assert np.abs(res["LSE"] - Lw).max() <= TOL_LSE
 
 
-@pytest.mark.parametrize("nblocks,nctas,per_tile", [(60, 8, 2), (60, 12, 3), (60, 16, 4), (120, 28, 7), (150, 60, 10)])
+@pytest.mark.parametrize("nblocks,nctas,per_tile", [(60, 8, 2), (60, 12, 3), (60, 16, 4), (120, 28, 7), (150, 60, 13)])
 def test_tiles_cut_into_n_runs_are_folded_by_their_ctas(api, ctx, orc, pkg, nblocks, nctas, per_tile):
     """One sequence on a chosen number of CTAs: every tile is cut into the same number of runs, each on a CTA of its own,
     and the tile is folded by those CTAs together (2, 3 and 4 runs take the few-slots path, more the general one). Every

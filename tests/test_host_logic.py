@@ -111,9 +111,9 @@ def test_planner_covers_every_unit_once(api, lengths, nq, nctas):
 
 
 def test_planner_gives_every_run_its_own_cta_when_the_step_is_small(api):
-    """Fewer output tiles than CTAs: a run per CTA, tiles cut into equal runs of about sqrt(units) units; with more work
+    """Fewer output tiles than CTAs: a run per CTA, tiles cut into equal runs of about 0.75 sqrt(units) units; with more work
     than that the shares are contiguous again and a tile straddles at most two CTAs' lists per cut."""
-    for nblocks, lo, hi in ((64, 6, 10), (256, 11, 17), (1024, 24, 37)):
+    for nblocks, lo, hi in ((64, 7, 10), (256, 17, 24), (1024, 30, 37)):
         st, items, cta_first = api.plan_preview([nblocks], 148)
         assert st.nitems == st.nctas and np.all(np.diff(cta_first[:st.nctas + 1]) == 1)
         per_tile = np.bincount(items[:, 7])
