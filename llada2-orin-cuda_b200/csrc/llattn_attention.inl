@@ -260,6 +260,15 @@ int llattn_create(int device, llattn_ctx** out) {
         return fail(LLATTN_ENOMEM, "create: cannot allocate the device error word");
     }
     if (int rc = ensure_kernel_attrs()) { cudaFree(c->err_word); delete c; return rc; }
+    // the largest grid a cooperative launch of the attention kernel accepts here: what fits on the device at once (fewer
+    // than one CTA per SM when the process was given only a part of the GPU)
+    int per_sm = 0;
+    if (cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, llattn::attn_tile_kernel<true>, llattn::ATTN_THREADS, llattn::ATTN_SMEM_BYTES) != cudaSuccess || per_sm < 1) {
+        cudaGetLastError();
+        cudaFree(c->err_word);
+        delete c;
+        return fail(LLATTN_ECUDA, "create: the attention kernel does not fit on an SM of device %d", device);
+    }
     *out = c;
     return LLATTN_OK;
 }
@@ -317,6 +326,7 @@ int llattn_plan_create(llattn_ctx* c, const llattn_seq* seqs, int nseq, int ncta
     // One CTA fits on an SM, and a CTA waits (bounded) for the other runs of the tiles it shares: every CTA of the launch
     // must be on an SM at the same time, so the grid never exceeds the SM count (the launch is a cooperative one).
     if (nctas <= 0 || nctas > c->num_sms) nctas = c->num_sms;
+    nctas = std::min(nctas, llattn::FOLD_MAX_SLOTS);       // a tile has at most one run per CTA, and the folding holds that many
     HostPlan hp;
     if (int rc = build_plan(seqs, nseq, nctas, hp)) return rc;
     if (hp.merge.size() > COUNTER_TILES) return fail(LLATTN_EINVAL, "plan_create: %zu output tiles, at most %d per call", hp.merge.size(), COUNTER_TILES);
