@@ -89,37 +89,19 @@ __global__ void __launch_bounds__(ATT_NTH, 1) attn_partial(Args a) {
     llattn::attn_tile_body<false>(p, (int(blockIdx.z) * a.nchunks + int(blockIdx.y)) * 4 + int(blockIdx.x));
 }
 
-// The reference's launch shape is kept (grid (4, 128 / COMB_ROWS, nb), a warp per query row): lanes 0..3 of the row's
-// warp each finish 32 of its 128 dims with the row routines of merge_kernel.cuh.
+// The reference's launch shape is kept (grid (4, 128 / COMB_ROWS, nb), a warp per query row); the warp folds its row with
+// the routine the attention kernel's own folding uses (merge_kernel.cuh: lane = 4 dims, the slots' reference exponents
+// and row sums fetched by the lanes in parallel, up to twelve slots' rows in flight).
 __global__ void __launch_bounds__(32 * COMB_ROWS)
 attn_combine(const float* Opart, const float* Mpart, const float* Lpart, int nchunks, int nblocks, int bpc, half* O,
              int8_t* q8, float* s8, int* sum8) {
     llattn::MergeOut o{};
     if (q8) { o.q8 = q8; o.s8 = s8; o.sum8 = sum8; }      // as engine/attn.cu:340-357: the int8 form replaces fp16 O
     else o.O16 = O;
-    const int kvh = blockIdx.x, jb = blockIdx.z, c = threadIdx.x & 31;
+    const int kvh = blockIdx.x, jb = blockIdx.z;
     const int r = blockIdx.y * COMB_ROWS + (threadIdx.x >> 5);
-    if (c >= 4) return;
-    const int nch = chunks_for(nblocks + jb, bpc), slot0 = (jb * 4 + kvh) * nchunks;
-    float M, den, v[32];
-    llattn::row_scale(Mpart, Lpart, slot0, nch, r, M, den);
-    const float inv = 1.f / den;
-    llattn::row_gather(Opart, Mpart, slot0, nch, r, M, c, v);
-#pragma unroll
-    for (int j = 0; j < 32; ++j) v[j] *= inv;
-    llattn::RowOut ro{size_t(jb) * BLK + (r >> 2), 4 * kvh + (r & 3), 0.f, 0};
-    if (q8) {
-        float m = llattn::absmax32(v);
-        m = fmaxf(m, __shfl_xor_sync(0xfu, m, 1));
-        m = fmaxf(m, __shfl_xor_sync(0xfu, m, 2));
-        ro.qscale = fmaxf(__fdiv_rn(m, 127.f), 1e-30f);
-    }
-    llattn::row_store(o, ro, c, v);
-    if (q8) {
-        ro.qsum += __shfl_xor_sync(0xfu, ro.qsum, 1);
-        ro.qsum += __shfl_xor_sync(0xfu, ro.qsum, 2);
-    }
-    if (c == 0) llattn::row_finish(o, ro, M, den);
+    const llattn::MergeDesc md{jb, kvh, (jb * 4 + kvh) * nchunks, chunks_for(nblocks + jb, bpc)};
+    llattn::fold_row_warp(Opart, Mpart, Lpart, md, r, int(threadIdx.x & 31), o);
 }
 
 __global__ void __launch_bounds__(llattn::COMMIT_THREADS)
