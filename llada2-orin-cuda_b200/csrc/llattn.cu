@@ -296,7 +296,7 @@ extern "C" int llattn_attention_static(const void* Q, const void* Kf, const void
     attn_tile_kernel<false><<<NKV * nchunks * nb, ATTN_THREADS, ATTN_SMEM_BYTES, as_stream(stream)>>>(p);
     CU(cudaGetLastError());
     MergeOut o{static_cast<half*>(O16), O32, LSE, q8, s8, sum8};
-    combine_ref_kernel<<<dim3(NKV, nb), MERGE_THREADS, 0, as_stream(stream)>>>(Opart, Mpart, Lpart, nchunks, nblocks, bpc, o);
+    combine_ref_kernel<<<dim3(NKV, QR / MERGE_ROWS, nb), MERGE_THREADS, 0, as_stream(stream)>>>(Opart, Mpart, Lpart, nchunks, nblocks, bpc, o);
     CU(cudaGetLastError());
     return LLATTN_OK;
 }

@@ -232,7 +232,7 @@ int llattn_attn_combine(const float* Opart, const float* Mpart, const float* Lpa
     MergeOut o{};
     if (q8) { o.q8 = q8; o.s8 = s8; o.sum8 = sum8; }       // as the reference: int8 form replaces the fp16 output
     else o.O16 = static_cast<half*>(O);
-    combine_ref_kernel<<<dim3(NKV, nb), MERGE_THREADS, 0, as_stream(stream)>>>(Opart, Mpart, Lpart, nchunks, nblocks, bpc, o);
+    combine_ref_kernel<<<dim3(NKV, QR / MERGE_ROWS, nb), MERGE_THREADS, 0, as_stream(stream)>>>(Opart, Mpart, Lpart, nchunks, nblocks, bpc, o);
     CU(cudaGetLastError());
     return LLATTN_OK;
 }

@@ -5,20 +5,20 @@
 // dense projection reads (per (token, head): scale = max|v| / 127 floored at 1e-30, q = clamp(rint(v / scale), +-127),
 // stored in the fragment order of engine/attn.cu:308-312, plus the integer row sum).
 //
-// One THREAD owns one query row (all 128 dims): that is how the attention kernel holds its accumulator (one tensor-memory
-// lane per row), so the same code finishes a row whether its values come from tensor memory (the attention kernel's
-// epilogue for a tile made of a single run) or from the partial slots in global memory (the reference-shaped operator
-// pair, combine_ref_kernel below). A row is handled 32 dims at a time. Tiles the attention kernel itself cut into several
-// runs are folded by the warp-per-row routines further down. The slots of a tile are always added in slot order, so the
-// result does not depend on which run finishes last.
+// Two forms. In the attention kernel's epilogue one THREAD owns one query row (that is how the kernel holds its
+// accumulator: one tensor-memory lane per row) and writes a row 32 dims at a time straight from tensor memory
+// (row_store, row_finish): a tile that a single run covers needs no folding. Everywhere partial slots have to be folded -
+// the attention kernel's split tiles, the reference-shaped operator pair, the allocation-free entry point, the source
+// shim - a WARP owns a row (fold_row_warp and friends, below). The slots of a tile are always added in slot order, so
+// the result does not depend on which run finishes last.
 #pragma once
 #include <cuda_fp16.h>
 #include "common.cuh"
 
 namespace llattn {
 
-constexpr int MERGE_ROWS = 128;               // rows per CTA of combine_ref_kernel: one thread each
-constexpr int MERGE_THREADS = MERGE_ROWS;
+constexpr int MERGE_ROWS = 8;                 // rows per CTA of combine_ref_kernel: one warp each
+constexpr int MERGE_THREADS = 32 * MERGE_ROWS;
 
 struct MergeOut {
     half* O16;
@@ -32,35 +32,6 @@ struct MergeOut {
 __device__ __forceinline__ int frag_pos(int c) {
     const int base = c & ~127, r = c & 127;
     return base + 32 * ((r >> 2) & 3) + 8 * (r >> 5) + 4 * ((r >> 4) & 1) + (r & 3);
-}
-
-// Reference maximum and weighted row sum of a row over the slots [slot0, slot0 + nslots).
-__device__ __forceinline__ void row_scale(const float* __restrict__ Mpart, const float* __restrict__ Lpart, int slot0, int nslots,
-                                          int row, float& M, float& den) {
-    M = -INFINITY;
-    for (int s = 0; s < nslots; ++s) M = fmaxf(M, Mpart[size_t(slot0 + s) * QR + row]);
-    den = 0.f;
-    for (int s = 0; s < nslots; ++s) {
-        const size_t i = size_t(slot0 + s) * QR + row;
-        den += exp2f(Mpart[i] - M) * Lpart[i];
-    }
-}
-
-// Dims [32 c, 32 c + 32) of the row's weighted, un-normalised sum over the slots, in dim order.
-__device__ __forceinline__ void row_gather(const float* __restrict__ Opart, const float* __restrict__ Mpart, int slot0, int nslots,
-                                           int row, float M, int c, float (&acc)[32]) {
-#pragma unroll
-    for (int j = 0; j < 32; ++j) acc[j] = 0.f;
-    for (int s = 0; s < nslots; ++s) {
-        const size_t i = size_t(slot0 + s) * QR + row;
-        const float w = exp2f(Mpart[i] - M);
-        const float4* src = reinterpret_cast<const float4*>(Opart + i * D + 32 * c);
-#pragma unroll
-        for (int g = 0; g < 8; ++g) {
-            const float4 v = src[g];
-            acc[4 * g] += w * v.x; acc[4 * g + 1] += w * v.y; acc[4 * g + 2] += w * v.z; acc[4 * g + 3] += w * v.w;
-        }
-    }
 }
 
 // Where a finished row goes: global token row, query head, and what is known before its values are walked.
@@ -260,42 +231,15 @@ __device__ __forceinline__ void fold_rows_few(const float* Opart, const float* M
     }
 }
 
-// Reference-shaped path: grid (4 kv heads, nb), 128 threads = the tile's rows; slots laid out [jb][kvh][nchunks] as
-// the reference's partial buffers, the live chunk count of block jb given by chunks_for(nblocks + jb, bpc).
-__device__ __forceinline__ void combine_ref_body(const float* __restrict__ Opart, const float* __restrict__ Mpart,
-                                                 const float* __restrict__ Lpart, int nchunks, int nblocks, int bpc, int kvh, int jb,
-                                                 int r, const MergeOut& o) {
-    const int nbl = nblocks + jb;
-    const int nch = nbl <= 0 ? 1 : (nbl + bpc - 1) / bpc;
-    const int slot0 = (jb * NKV + kvh) * nchunks;
-    float M, den;
-    row_scale(Mpart, Lpart, slot0, nch, r, M, den);
-    const float inv = 1.f / den;
-    RowOut ro{size_t(jb) * BLK + (r >> 2), 4 * kvh + (r & 3), 0.f, 0};
-    float v[32];
-    if (o.q8) {
-        float m = 0.f;
-        for (int c = 0; c < 4; ++c) {
-            row_gather(Opart, Mpart, slot0, nch, r, M, c, v);
-#pragma unroll
-            for (int j = 0; j < 32; ++j) v[j] *= inv;
-            m = fmaxf(m, absmax32(v));
-        }
-        ro.qscale = fmaxf(__fdiv_rn(m, 127.f), 1e-30f);
-    }
-    for (int c = 0; c < 4; ++c) {
-        row_gather(Opart, Mpart, slot0, nch, r, M, c, v);
-#pragma unroll
-        for (int j = 0; j < 32; ++j) v[j] *= inv;
-        row_store(o, ro, c, v);
-    }
-    row_finish(o, ro, M, den);
-}
-
+// Reference-shaped path (the operator pair on caller-owned partial buffers, and the allocation-free entry point): slots
+// laid out [jb][kvh][nchunks] as the reference's partial buffers, the live chunk count of block jb given by
+// chunks_for(nblocks + jb, bpc). Grid (4 kv heads, 128 / MERGE_ROWS, nb), a warp per query row.
 __global__ void __launch_bounds__(MERGE_THREADS)
 combine_ref_kernel(const float* __restrict__ Opart, const float* __restrict__ Mpart, const float* __restrict__ Lpart,
                    int nchunks, int nblocks, int bpc, MergeOut o) {
-    combine_ref_body(Opart, Mpart, Lpart, nchunks, nblocks, bpc, blockIdx.x, blockIdx.y, threadIdx.x, o);
+    const int kvh = blockIdx.x, jb = blockIdx.z, nbl = nblocks + jb;
+    const MergeDesc md{jb, kvh, (jb * NKV + kvh) * nchunks, nbl <= 0 ? 1 : (nbl + bpc - 1) / bpc};
+    fold_row_warp(Opart, Mpart, Lpart, md, int(blockIdx.y) * MERGE_ROWS + int(threadIdx.x >> 5), int(threadIdx.x & 31), o);
 }
 
 }  // namespace llattn
