@@ -3,7 +3,7 @@ directory and generate from a seeded prompt, the way the reference's server bind
 (`server/server.py:62-71,94-117`: `llada_init`, `llada_generate`, `llada_stats` over ctypes). Prints one JSON line.
 The engine ends the process on a malformed directory (`exit(1)` in its loader), which is why it runs in a child.
 
-    python tests/engine_run.py <libllada*.so> <engine directory> <prompt tokens> <new tokens> [<vocab>]
+    python tests/engine_run.py <libllada*.so> <engine directory> <prompt tokens> <new tokens> [<vocab> [<max context tokens>]]
 """
 import ctypes
 import json
@@ -16,6 +16,7 @@ import numpy as np
 def main():
     lib_path, directory, nprompt, max_new = sys.argv[1], sys.argv[2], int(sys.argv[3]), int(sys.argv[4])
     vocab = int(sys.argv[5]) if len(sys.argv) > 5 else 4096
+    max_ctx = int(sys.argv[6]) if len(sys.argv) > 6 else 4096
     lib = ctypes.CDLL(lib_path)
     cb_t = ctypes.CFUNCTYPE(None, ctypes.POINTER(ctypes.c_int), ctypes.c_int, ctypes.c_void_p)
     lib.llada_init.restype = ctypes.c_void_p
@@ -26,7 +27,7 @@ def main():
                                    ctypes.POINTER(ctypes.c_int), ctypes.c_int, cb_t, ctypes.c_void_p]
     lib.llada_stats.argtypes = [ctypes.c_void_p, ctypes.POINTER(ctypes.c_double)]
     t0 = time.time()
-    h = lib.llada_init(directory.encode(), 4096)
+    h = lib.llada_init(directory.encode(), max_ctx)
     load_s = time.time() - t0
     prompt = np.random.default_rng(7).integers(0, vocab, nprompt).astype(np.int32)
     blocks = []

@@ -21,12 +21,12 @@ REF = os.path.join(ROOT, "oracle", "_ref")
 VOCAB, NPROMPT, NEW = 4096, 104, 56
 
 
-def run_engine(lib, directory, dump=None):
+def run_engine(lib, directory, dump=None, nprompt=NPROMPT, new=NEW, max_ctx=4096):
     env = dict(os.environ)
     if dump:
         env["LLADA_DUMPX"] = dump                        # engine/decode.cu:329-336: the readout's input, every step
-    p = subprocess.run([sys.executable, os.path.join(ROOT, "tests", "engine_run.py"), lib, directory, str(NPROMPT),
-                        str(NEW), str(VOCAB)], capture_output=True, text=True, timeout=600, env=env)
+    p = subprocess.run([sys.executable, os.path.join(ROOT, "tests", "engine_run.py"), lib, directory, str(nprompt),
+                        str(new), str(VOCAB), str(max_ctx)], capture_output=True, text=True, timeout=900, env=env)
     assert p.returncode == 0, f"{os.path.basename(lib)} ended with {p.returncode}:\n{p.stderr[-2000:]}"
     return json.loads(p.stdout.strip().splitlines()[-1])
 
@@ -111,3 +111,32 @@ def test_first_step_hidden_state_matches_the_reference_engine(tmp_path, capsys):
         print(f"\n[engine, 1 dense layer] first step: hidden state rel-L2 {rel:.3e}, largest code difference "
               f"{int(np.abs(qa - qb).max())}, codes equal {float((qa == qb).mean()):.3f}")
     assert rel <= 3e-2 and np.abs(qa - qb).max() <= 6
+
+
+def test_decode_at_32k_context_through_the_whole_engine(tmp_path, capsys):
+    """Twenty layers (the model's depth), a 32,768-token prompt, then one block decoded on top of the reused prefix (the
+    second call: no prefill in its time). The engine around the attention is the reference's own in both runs, so the
+    difference in decode time is the attention kernels': the reference's spread a step's context over 16 CTAs, the
+    drop-in's over the whole GPU."""
+    dropin, ref_lib = os.path.join(REF, "libllada_dropin.so"), os.path.join(REF, "libllada_ref.so")
+    if not (os.path.exists(dropin) and os.path.exists(ref_lib)):
+        pytest.skip("oracle/_ref/libllada_{dropin,ref}.so not built (make -C oracle ref dropin REF=<reference checkout>)")
+    ed = importlib.import_module(PKG_NAME + ".engine_dir")
+    d = str(tmp_path / "deep")
+    ed.write_engine_dir(d, layers=20, dense_layers=1, vocab=VOCAB, seed=5)
+    assert ed.check_layout(d) == []
+    nprompt, new = 32768 + 8, 24
+    mine = run_engine(dropin, d, nprompt=nprompt, new=new, max_ctx=33792)
+    ref = run_engine(ref_lib, d, nprompt=nprompt, new=new, max_ctx=33792)
+    for r in (mine, ref):
+        first, second = r["runs"]
+        assert len(first["ids"]) == new and len(second["ids"]) == new
+        assert first["reused_blocks"] == 0 and second["reused_blocks"] == 1024 and second["kv_gb"] > 0.35
+    step = lambda r: r["runs"][1]["seconds"] / (r["runs"][1]["steps"] - r["runs"][0]["steps"])
+    with capsys.disabled():
+        print(f"\n[engine, 20 layers, 32 K context] decode of one block over a reused prefix: drop-in "
+              f"{mine['runs'][1]['seconds']:.3f} s ({1e3 * step(mine):.2f} ms per denoising step), reference kernels "
+              f"{ref['runs'][1]['seconds']:.3f} s ({1e3 * step(ref):.2f} ms per step); prefill of the prompt "
+              f"{mine['runs'][0]['seconds'] - mine['runs'][1]['seconds']:.2f} s against "
+              f"{ref['runs'][0]['seconds'] - ref['runs'][1]['seconds']:.2f} s")
+    assert step(mine) < 0.6 * step(ref)
