@@ -128,6 +128,33 @@ def test_planner_gives_every_run_its_own_cta_when_the_step_is_small(api):
     assert (items[:, 4] + items[:, 5]).min() >= 12
 
 
+def test_planner_invariants_on_random_batches(api):
+    """300 seeded random batches (1 .. 40 sequences, 0 .. 1100 blocks, 1 .. 3 query blocks, 1 .. 148 CTAs): every unit is
+    covered exactly once and in order, cuts fall on tile boundaries, runs never outnumber tiles + CTAs (the capacity a
+    plan reserves so that updates never allocate), a CTA holds at most one run of a tile (the folding relies on it)."""
+    g = np.random.default_rng(2024)
+    for _ in range(300):
+        nseq = int(g.integers(1, 41))
+        lengths = [int(x) for x in g.choice([0, 1, 3, 7, 31, 64, 255, 256, 1024, 1100], nseq)]
+        nq = [int(x) for x in g.integers(1, 4, nseq)]
+        nctas = int(g.choice([1, 2, 7, 37, 64, 148]))
+        st, items, cta_first = api.plan_preview(lengths, nctas, nq)
+        tiles = 4 * sum(nq)
+        assert 1 <= st.nctas <= nctas and st.nitems <= tiles + nctas
+        assert np.array_equal(items[:, 6], np.arange(st.nitems)) and np.all(items[:, 3] % api.tile_units() == 0)
+        done = {}
+        for seq, qb, kvh, rec0, nrec, fresh, slot, tile in items:
+            c = done.setdefault((seq, qb, kvh), [0, 0, tile])
+            assert rec0 == c[0] and c[1] == 0 and tile == c[2] and nrec + fresh > 0
+            c[0] += nrec; c[1] += fresh
+        assert len(done) == tiles
+        for (seq, qb, kvh), (nrec, fresh, _) in done.items():
+            assert nrec == lengths[seq] + qb and fresh == 1
+        for c in range(st.nctas):
+            mine = items[cta_first[c]:cta_first[c + 1], 7]
+            assert len(set(mine.tolist())) == len(mine)
+
+
 def test_sharding_balances_ragged_requests(pkg):
     sh, wl = pkg.sharding, pkg.workload
     lens = wl.ragged_lengths(256)
