@@ -261,6 +261,26 @@ def test_tiles_cut_into_n_runs_are_folded_by_their_ctas(api, ctx, orc, pkg, nblo
     assert one["stats"].nitems == 4 and rel_l2(one["O32"], res["O32"]) <= 2 * TOL_L2
 
 
+def test_random_small_batches_on_random_grids(api, ctx, orc, pkg):
+    """Ten seeded random batches (1 .. 9 sequences, 0 .. 90 blocks, one or two query blocks) on 3, 11, 40 or all CTAs:
+    whatever mixture of whole tiles, tiles cut in two and tiles cut in many the planner makes of them, every CTA's waits
+    for its tiles' other runs end, and the outputs match the oracle."""
+    g = np.random.default_rng(77)
+    for b in range(10):
+        nseq = int(g.integers(1, 10))
+        cases, want = [], []
+        for i in range(nseq):
+            n, nq = int(g.choice([0, 1, 2, 5, 13, 32, 47, 90])), int(g.integers(1, 3))
+            Q, Kf, Vf, cache, maxb = make_case(pkg.workload, orc, n, nq=nq, seq=700 + 16 * b + i)
+            cases.append((Q, Kf, Vf, cache, maxb, n))
+            want.append(orc.attention(Q, Kf, Vf, cache, maxb, n, dq_mode=1))
+        Ow = np.concatenate([w[0] for w in want]); Lw = np.concatenate([w[1] for w in want])
+        nctas = int(g.choice([3, 11, 40, 0]))
+        res = run_batched(api, ctx, cases, nctas=nctas)
+        assert relmax(res["O32"], Ow) <= tol_o(90) and rel_l2(res["O32"], Ow) <= TOL_L2, (b, nctas)
+        assert np.abs(res["LSE"] - Lw).max() <= TOL_LSE, (b, nctas)
+
+
 def test_many_short_items_per_cta(api, ctx, orc, pkg):
     """48 short sequences on 5 CTAs: every CTA walks about 40 items, so the per-item hand-overs (query rows into tensor
     memory, accumulator release, partial slots) run back to back, with tiles of 1 to 4 units."""
