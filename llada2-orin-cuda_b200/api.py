@@ -175,6 +175,28 @@ def kv_commit_paged(Kf, Vf, pool, pages, stream=None) -> None:
     _check(lib().llattn_kv_commit_paged(_ptr(Kf), _ptr(Vf), _ptr(pool), _ptr(pages), nb, _stream(stream)))
 
 
+def commit_needs_forward(final_ids, last_forward_ids) -> bool:
+    """The decoder's commit policy (Decoder::commit, engine/decode.cu:267-280): when the last denoising forward of a
+    block ran on exactly the ids the block ends with, the fresh K/V that forward left behind are the block's final K/V
+    and only the quantiser has to run (`kv_commit` on them); otherwise one more forward pass on the final ids comes
+    first (`qkv_prepare_commit` is that pass's producer and commit in one kernel). Host logic only."""
+    a, b = [int(x) for x in final_ids], None if last_forward_ids is None else [int(x) for x in last_forward_ids]
+    return b is None or len(a) != len(b) or a != b
+
+
+def commit_block(final_ids, last_forward_ids, Kf, Vf, cache, max_blocks: int, blk: int, forward=None, stream=None) -> bool:
+    """Commit one decoded block the way the reference decoder does. Kf, Vf: the fresh fp16 K/V [1][32][4][128] of the
+    last denoising forward. If that forward did not run on `final_ids`, `forward(final_ids)` is called first and must
+    refill Kf and Vf (raises if it is needed and missing). Returns True when only the quantiser ran."""
+    kv_only = not commit_needs_forward(final_ids, last_forward_ids)
+    if not kv_only:
+        if forward is None:
+            raise ValueError("the last forward did not run on the final ids: a forward pass is needed before the commit")
+        forward(final_ids)
+    kv_commit(Kf, Vf, cache, max_blocks, blk, stream)
+    return kv_only
+
+
 # ------------------------------------------------------------------ consumer
 
 def dense_w4a8(W, q, s, qsum, Y, err_word=None, stream=None) -> None:

@@ -137,6 +137,30 @@ def test_commit_bit_exact_vs_oracle(api, orc, pkg, golden_dir, src):
         assert torch.equal(ref, got)
 
 
+def test_commit_block_follows_the_decoder_policy(api, orc, pkg):
+    """Decoder::commit (engine/decode.cu:267-280): the quantiser alone when the last forward already ran on the block's
+    final ids, one more forward (here: a callback that refills the fresh K/V) before it otherwise."""
+    K, V = pkg.workload.context_blocks(2, seq=31)
+    dK, dV = dev(K[:1]), dev(V[:1])
+    maxb = 5
+    cache = torch.zeros((4, maxb, orc.REC_BYTES), dtype=torch.uint8, device="cuda")
+    ids = list(range(500, 532))
+    assert api.commit_block(ids, list(ids), dK, dV, cache, maxb, 1) is True
+    calls = []
+
+    def forward(final_ids):
+        calls.append(list(final_ids))
+        dK.copy_(dev(K[1:2])); dV.copy_(dev(V[1:2]))
+
+    stale = list(ids); stale[3] = 156895
+    assert api.commit_block(ids, stale, dK, dV, cache, maxb, 2, forward=forward) is False and calls == [ids]
+    torch.cuda.synchronize()
+    want = np.zeros((4, maxb, orc.REC_BYTES), np.uint8)
+    orc.kv_commit(K[:1], V[:1], want, maxb, 1)
+    orc.kv_commit(K[1:2], V[1:2], want, maxb, 2)
+    assert np.array_equal(cache.cpu().numpy(), want)
+
+
 def test_commit_paged(api, orc, pkg):
     K, V = pkg.workload.context_blocks(9, seq=8)
     want = np.zeros((4, 9, orc.REC_BYTES), np.uint8)

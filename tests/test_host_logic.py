@@ -179,3 +179,14 @@ def test_workload_is_reproducible_and_shaped(pkg):
     assert 6.0 < big[..., out].std() < 10.0 and 0.9 < big[..., rest].std() < 1.1
     assert wl.algorithmic_bytes(1024) == 592 * 32768 + 327680
     assert wl.algorithmic_flops(1024) == 262144 * (32768 + 32)
+
+
+def test_decoder_commit_policy(api):
+    """engine/decode.cu:267-280: KV-only commit exactly when the last forward ran on the block's final ids."""
+    blk = list(range(100, 132))
+    assert api.commit_needs_forward(blk, None) and api.commit_needs_forward(blk, [])
+    assert not api.commit_needs_forward(blk, list(blk)) and not api.commit_needs_forward(np.array(blk), tuple(blk))
+    other = list(blk); other[17] = 156895
+    assert api.commit_needs_forward(blk, other) and api.commit_needs_forward(blk, blk[:31])
+    with pytest.raises(ValueError):
+        api.commit_block(blk, other, None, None, None, 4, 0)        # a forward pass is needed and none was given
